@@ -12,7 +12,8 @@ every position and every tensor of the group.
 
 Pages come back in two ways: all of a request's pages when it is closed, and, in a window
 group, every page that lies wholly behind the window of the next query, as soon as the
-request's length has moved past it.  Returned pages are reused first (LIFO).
+request's length has moved past it (a window group that keeps the sequence's first positions
+visible holds on to their pages).  Returned pages are reused first (LIFO).
 
 Beside the pages each request holds one state slot: an index into fixed-size float32 state
 tensors ``[max_seqs, *state_shape]`` of the positions whose mixers ask for state.  The dense
@@ -61,6 +62,13 @@ class CacheGroup:
     @property
     def chunk(self) -> int | None:
         return self.spec.chunk if self.spec.kind == "chunk" else None
+
+    @property
+    def kept_pages(self) -> int:
+        """Pages at the start of a sequence that a window never gives back (they hold its kept first positions)."""
+        if self.window is None or self.spec.keep_first <= 0:
+            return 0
+        return (self.spec.keep_first + self.page_size - 1) // self.page_size
 
     def first_needed_key(self, length: int) -> int:
         """The lowest position that a query at position ``length`` or later can still read."""
@@ -125,6 +133,8 @@ class CacheManager:
                 raise ValueError(f"schedule position {pos}: a chunk cache needs a positive chunk")
             if spec.kind == "window" and (spec.window is None or spec.window <= 0):
                 raise ValueError(f"schedule position {pos}: a window cache needs a positive window")
+            if spec.keep_first < 0 or (spec.keep_first and spec.kind != "window"):
+                raise ValueError(f"schedule position {pos}: kept first positions go with a window cache")
             stored = spec.stored()
             if not stored or any(t.heads <= 0 or t.width <= 0 for t in stored) or \
                     len({t.name for t in stored}) != len(stored):
@@ -223,7 +233,8 @@ class CacheManager:
             # the keys from its block's first position on
             releasable = g.first_needed_key(seq.length) // self.page_size
             pages = seq.pages[g.index]
-            for logical in range(seq.first_live[g.index], min(releasable, len(pages))):
+            # first_live: the first page behind the kept ones that is still held
+            for logical in range(max(seq.first_live[g.index], g.kept_pages), min(releasable, len(pages))):
                 if pages[logical] >= 0:
                     g.pool.free(pages[logical])
                     pages[logical] = -1
@@ -284,7 +295,7 @@ class CacheManager:
                 out.append(full)
             else:
                 span = reach + chunk + self.page_size  # what is still read, the step's tokens, a partial page
-                out.append(min(full, (span + self.page_size - 1) // self.page_size + 1))
+                out.append(min(full, (span + self.page_size - 1) // self.page_size + 1 + g.kept_pages))
         return out
 
     def check_invariants(self) -> None:

@@ -472,3 +472,177 @@ class ZifuzenConfig:
         if self.eos_token_id:
             out["eos_token_id"] = list(self.eos_token_id)
         return out
+
+
+@dataclass(frozen=True)
+class RenadraLayer:
+    """One entry of ``layers``: the mixer's ``type``, its sizes and constants as config.json gives them, and the
+    feed-forward (None: the layer has none)."""
+
+    type: str
+    mixer: dict
+    mlp: dict | None
+
+    MIXERS = ("attention", "hgrn2", "parallel")
+
+
+@dataclass(frozen=True)
+class RenadraConfig:
+    """config.json of the ``Renadra`` decoder: ``vocab``, ``width``, ``norm.eps``, ``embedding`` (``scale`` and an
+    optional ``bigram`` table: ``buckets``, ``mul_prev``, ``mul_cur``), a list of layers and an optional ``loop``
+    (``start``, ``stop``, ``times``: layers start .. stop - 1 run ``times`` times in a row with the same weights).
+    A layer names its mixer (``attention``: rotated queries and keys in neighbouring pairs, unit-RMS values, a window,
+    softmax; ``hgrn2``: a matrix memory per head whose forget gate also decides what is written; ``parallel``: a
+    ``left`` attention without a softmax whose values are its unrotated keys, beside a ``right`` linear attention with
+    a constant decay per head) and its dense feed-forward (or null).  Every size and constant is read from here."""
+
+    vocab: int
+    width: int
+    norm_eps: float
+    embedding_scale: float
+    bigram: dict | None
+    layers: tuple[RenadraLayer, ...]
+    loop: dict | None = None
+    max_position_embeddings: int = 1 << 20
+    eos_token_id: tuple[int, ...] = ()
+    architectures: tuple[str, ...] = ("Renadra",)
+
+    ARCHITECTURE = "Renadra"
+
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @staticmethod
+    def _check_rot(m: dict, where: str, dim: int, scaling: bool) -> None:
+        rot = _section(m, "rot", where)
+        where_r = where + "rot: "
+        dims = _sized(rot, "dims", where_r)
+        if _number(rot, "base", where_r) <= 1:
+            raise ConfigError(f"config.json: {where_r}'base' must be above 1")
+        if dims % 2 or dims > dim:
+            raise ConfigError(f"config.json: {where_r}'dims' must be even and at most 'dim' ({dim}), got {dims}")
+        if rot.get("scaling") is not None:
+            if not scaling:
+                raise ConfigError(f"config.json: {where_r}'scaling' is not part of this mixer")
+            s = _section(rot, "scaling", where_r)
+            for key in ("factor", "original", "fast", "slow"):
+                if _number(s, key, where_r + "scaling: ") <= 0:
+                    raise ConfigError(f"config.json: {where_r}scaling: '{key}' must be positive")
+
+    @classmethod
+    def _check_attention(cls, m: dict, where: str, left: bool) -> None:
+        for key in ("heads", "kv_heads", "dim", "vdim"):
+            _sized(m, key, where)
+        if m["heads"] % m["kv_heads"]:
+            raise ConfigError(f"config.json: {where}'heads' ({m['heads']}) must be a multiple of 'kv_heads' "
+                              f"({m['kv_heads']})")
+        _number(m, "scale", where)
+        cls._check_rot(m, where, m["dim"], scaling=left)
+        mask = _section(m, "mask", where)
+        _sized(mask, "size", where + "mask: ")
+        if left:
+            if m["vdim"] != m["dim"]:
+                raise ConfigError(f"config.json: {where}'vdim' ({m['vdim']}) must equal 'dim' ({m['dim']}): the values "
+                                  f"are the keys")
+            keep = mask.get("keep_first", 0)
+            if isinstance(keep, bool) or not isinstance(keep, int) or keep < 0:
+                raise ConfigError(f"config.json: {where}mask: 'keep_first' must be a non-negative integer, got {keep!r}")
+            if _number(m, "softcap", where) <= 0:
+                raise ConfigError(f"config.json: {where}'softcap' must be positive")
+        elif mask.get("keep_first"):
+            raise ConfigError(f"config.json: {where}mask: 'keep_first' is not part of this mixer")
+
+    @staticmethod
+    def _check_memory(m: dict, where: str, decay: bool) -> None:
+        for key in ("heads", "dim", "vdim"):
+            _sized(m, key, where)
+        if decay:
+            rates = m.get("decay")
+            if not isinstance(rates, (list, tuple)) or len(rates) != m["heads"] or not all(
+                    isinstance(r, (int, float)) and not isinstance(r, bool) and 0 <= r <= 1 for r in rates):
+                raise ConfigError(f"config.json: {where}'decay' must list a number between 0 and 1 for each of the "
+                                  f"{m['heads']} heads")
+
+    @classmethod
+    def from_dict(cls, d: dict[str, Any]) -> "RenadraConfig":
+        layers_raw = d.get("layers")
+        if not isinstance(layers_raw, (list, tuple)) or not layers_raw:
+            raise ConfigError("config.json: key 'layers' must be a non-empty list")
+        layers = []
+        for i, entry in enumerate(layers_raw):
+            where = f"layers[{i}]: "
+            if not isinstance(entry, dict) or entry.get("type") not in RenadraLayer.MIXERS:
+                raise ConfigError(f"config.json: {where}'type' must be one of {list(RenadraLayer.MIXERS)}, "
+                                  f"got {entry.get('type') if isinstance(entry, dict) else entry!r}")
+            mixer = _section(entry, "mixer", where)
+            where_m = where + "mixer: "
+            if entry["type"] == "attention":
+                cls._check_attention(mixer, where_m, left=False)
+            elif entry["type"] == "hgrn2":
+                cls._check_memory(mixer, where_m, decay=False)
+            else:
+                cls._check_attention(_section(mixer, "left", where_m), where_m + "left: ", left=True)
+                cls._check_memory(_section(mixer, "right", where_m), where_m + "right: ", decay=True)
+                _number(mixer, "left_scale", where_m)
+                _number(mixer, "right_scale", where_m)
+            mlp = entry.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict):
+                    raise ConfigError(f"config.json: {where}'mlp' must be an object or null")
+                if mlp.get("kind", "dense") != "dense":
+                    raise ConfigError(f"config.json: {where}mlp: 'kind' must be 'dense', got {mlp.get('kind')!r}")
+                _sized(mlp, "ff", where + "mlp: ")
+            layers.append(RenadraLayer(entry["type"], copy.deepcopy(mixer), None if mlp is None else copy.deepcopy(mlp)))
+        embedding = _section(d, "embedding", "")
+        bigram = embedding.get("bigram")
+        if bigram is not None:
+            bigram = _section(embedding, "bigram", "embedding: ")
+            _sized(bigram, "buckets", "embedding: bigram: ")
+            for key in ("mul_prev", "mul_cur"):
+                if isinstance(bigram.get(key), bool) or not isinstance(bigram.get(key), int) or bigram[key] < 0:
+                    raise ConfigError(f"config.json: embedding: bigram: '{key}' must be a non-negative integer, "
+                                      f"got {bigram.get(key)!r}")
+            bigram = dict(bigram)
+        loop = d.get("loop")
+        if loop is not None:
+            loop = _section(d, "loop", "")
+            times = _sized(loop, "times", "loop: ")
+            start, stop = loop.get("start"), loop.get("stop")
+            if not all(isinstance(v, int) and not isinstance(v, bool) for v in (start, stop)) or \
+                    not 0 <= start < stop <= len(layers):
+                raise ConfigError(f"config.json: loop: 'start' and 'stop' must satisfy 0 <= start < stop <= "
+                                  f"{len(layers)}, got {start!r} and {stop!r}")
+            loop = {"start": start, "stop": stop, "times": times}
+        eos = d.get("eos_token_id")
+        eos = () if eos is None else ((eos,) if isinstance(eos, int) else tuple(eos))
+        cfg = cls(
+            vocab=_sized(d, "vocab", ""),
+            width=_sized(d, "width", ""),
+            norm_eps=_number(_section(d, "norm", ""), "eps", "norm: "),
+            embedding_scale=_number(embedding, "scale", "embedding: "),
+            bigram=bigram,
+            layers=tuple(layers),
+            loop=loop,
+            max_position_embeddings=_optional(d, "max_position_embeddings", int, 1 << 20),
+            eos_token_id=eos,
+        )
+        if cfg.norm_eps <= 0:
+            raise ConfigError("config.json: norm: 'eps' must be positive")
+        return cfg
+
+    def to_dict(self) -> dict[str, Any]:
+        embedding: dict[str, Any] = {"scale": self.embedding_scale}
+        if self.bigram is not None:
+            embedding["bigram"] = dict(self.bigram)
+        out = {"architecture": self.ARCHITECTURE, "vocab": self.vocab, "width": self.width,
+               "norm": {"eps": self.norm_eps}, "embedding": embedding,
+               "layers": [{"type": l.type, "mixer": copy.deepcopy(l.mixer),
+                           "mlp": None if l.mlp is None else copy.deepcopy(l.mlp)} for l in self.layers]}
+        if self.loop is not None:
+            out["loop"] = dict(self.loop)
+        if self.max_position_embeddings != 1 << 20:
+            out["max_position_embeddings"] = self.max_position_embeddings
+        if self.eos_token_id:
+            out["eos_token_id"] = list(self.eos_token_id)
+        return out

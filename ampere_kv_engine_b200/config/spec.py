@@ -72,11 +72,14 @@ class ScheduleEntry:
     ``layer`` indexes :attr:`ModelSpec.layers` (a layer may appear more than once: its
     weights are shared, each appearance has a cache of its own unless ``cache_of`` says
     otherwise).  ``cache_of`` names an earlier position of the schedule whose cache this
-    position reads instead of writing one of its own.
+    position reads instead of writing one of its own.  ``add_embedding``: the embedding's output (the
+    residual stream as it was before the first position) is added to the stream right before this position runs,
+    as a model does that sends the stream through a run of layers again.
     """
 
     layer: int
     cache_of: int | None = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

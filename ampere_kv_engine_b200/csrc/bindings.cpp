@@ -720,7 +720,8 @@ void scored_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
                       const Tensor& tile_q0, const Tensor& tile_nq, const OptTensor& partials, int64_t num_tiles,
                       int64_t q_tile, int64_t num_splits, int64_t num_heads, int64_t num_kv_heads, int64_t v_dim,
                       int64_t window, int64_t chunk, double scale, double softcap, const OptTensor& slopes,
-                      const OptTensor& gate, const OptTensor& status, int64_t kernel) {
+                      const OptTensor& gate, const OptTensor& status, int64_t kernel, int64_t keep_first,
+                      bool sigmoid_weights, const OptTensor& head_bias, double out_scale) {
   check_cuda(q, "q");
   check_cuda(out, "out");
   check_same(q, out, "q", "out");
@@ -794,6 +795,16 @@ void scored_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   sp.v_row_stride = v_cache.size(3);
   sp.softcap = (float)softcap;
   sp.chunk = (int)chunk;
+  AKV_CHECK(keep_first >= 0 && (keep_first == 0 || (window > 0 && chunk == 0)),
+            "scored_attention: keep_first goes with a window and without blocks");
+  sp.keep_first = (int)keep_first;
+  sp.sigmoid_weights = sigmoid_weights ? 1 : 0;
+  if (head_bias.has_value()) {
+    AKV_CHECK(sigmoid_weights, "scored_attention: head_bias is read with sigmoid_weights only");
+    check_f32(*head_bias, "head_bias", num_heads);
+    sp.head_bias = head_bias->data_ptr<float>();
+  }
+  sp.out_scale = (float)out_scale;
   c10::cuda::CUDAGuard guard(q.device());
   check_launch(akv::launch_scored_attention(sp, stream_of(q)), "scored_attention");
 }
@@ -1164,6 +1175,208 @@ void delta_scan(const Tensor& qkv, const Tensor& coef, const Tensor& x, const Te
   check_launch(akv::launch_delta_scan(p, stream_of(x)), "delta_scan");
 }
 
+// Linear attention with a decaying matrix memory (see launchers.h).  x: one product's output; state
+// [slots, floats per slot] float32 (a view whose rows may be wider than this mixer's share: its stride is passed on).
+void linear_scan(const Tensor& x, Tensor& state, const Tensor& cu_q, const Tensor& state_slots, Tensor& out,
+                 int64_t num_heads, int64_t head_dim, int64_t v_dim, int64_t mode, int64_t q_off, int64_t k_off,
+                 int64_t v_off, const OptTensor& gate_bias, const OptTensor& lower, const OptTensor& decay) {
+  check_cuda(x, "x");
+  AKV_CHECK(x.dim() == 2, "x must be [tokens, columns]");
+  AKV_CHECK(num_heads > 0 && akv::linear_scan_state_floats((int)num_heads, (int)head_dim, (int)v_dim) > 0,
+            "linear_scan: ", num_heads, " heads of ", head_dim, " x ", v_dim, " are outside what the kernel takes (each up to ",
+            (int64_t)akv::kLinearScanMaxDim, ")");
+  const int64_t n = x.size(0), qk = num_heads * head_dim, vw = num_heads * v_dim;
+  AKV_CHECK(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + qk <= x.size(1) && k_off + qk <= x.size(1) &&
+            v_off + vw <= x.size(1), "linear_scan: the q, k and v columns must lie inside x");
+  AKV_CHECK(state.is_cuda() && state.scalar_type() == at::kFloat && state.dim() == 2 && state.stride(1) == 1 &&
+            state.size(1) >= akv::linear_scan_state_floats((int)num_heads, (int)head_dim, (int)v_dim),
+            "state must be float32 [slots, at least the memory's floats] with unit stride in a row");
+  check_i32(cu_q, "cu_q");
+  const int64_t seqs = cu_q.numel() - 1;
+  check_i32(state_slots, "state_slots", seqs);
+  check_f32(out, "out", n * vw);
+  akv::LinearScanParams p{};
+  p.x = x.data_ptr();
+  p.x_stride = x.size(1);
+  p.q_off = (int)q_off;
+  p.k_off = (int)k_off;
+  p.v_off = (int)v_off;
+  if (gate_bias.has_value()) {
+    check_f32(*gate_bias, "gate_bias", qk);
+    p.gate_bias = gate_bias->data_ptr<float>();
+  }
+  if (lower.has_value()) {
+    check_f32(*lower, "lower", qk);
+    p.lower = lower->data_ptr<float>();
+  }
+  if (decay.has_value()) {
+    check_f32(*decay, "decay", num_heads);
+    p.decay = decay->data_ptr<float>();
+  }
+  AKV_CHECK(mode == akv::kGatedWrite ? lower.has_value() : (mode == akv::kConstantDecay && decay.has_value()),
+            "linear_scan: mode 0 needs lower, mode 1 needs decay");
+  p.state = state.data_ptr<float>();
+  p.state_stride = state.stride(0);
+  p.cu_q = cu_q.data_ptr<int>();
+  p.state_slots = state_slots.data_ptr<int>();
+  p.out = out.data_ptr<float>();
+  p.num_tokens = n;
+  p.num_seqs = (int)seqs;
+  p.num_heads = (int)num_heads;
+  p.head_dim = (int)head_dim;
+  p.v_dim = (int)v_dim;
+  p.mode = (int)mode;
+  p.dtype = dtype_code(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_linear_scan(p, stream_of(x)), "linear_scan");
+}
+
+void group_norm_gate(const Tensor& in, Tensor& out, const Tensor& weight, int64_t group, double eps, double factor,
+                     const OptTensor& x, int64_t gate_off) {
+  check_cuda(in, "in");
+  check_cuda(out, "out");
+  AKV_CHECK(in.scalar_type() == at::kFloat && in.dim() == 2, "in must be float32 [tokens, width]");
+  const int64_t n = in.size(0), width = in.size(1);
+  AKV_CHECK(out.numel() == n * width, "out must be [tokens, width]");
+  AKV_CHECK(group >= 1 && width % group == 0, "group_norm_gate: the group (", group, ") must divide the width (", width, ")");
+  check_cuda(weight, "weight");
+  AKV_CHECK(weight.scalar_type() == at::kFloat && (weight.numel() == group || weight.numel() == width),
+            "weight must be float32 with a group's or the whole width's entries");
+  const void* x_ptr = nullptr;
+  int64_t x_stride = 0;
+  if (x.has_value()) {
+    check_cuda(*x, "x");
+    check_same(*x, out, "x", "out");
+    AKV_CHECK(x->dim() == 2 && x->size(0) == n && gate_off >= 0 && gate_off + width <= x->size(1),
+              "the gate columns must lie inside x");
+    x_ptr = x->data_ptr();
+    x_stride = x->size(1);
+  }
+  c10::cuda::CUDAGuard guard(in.device());
+  check_launch(akv::launch_group_norm_gate(in.data_ptr<float>(), out.data_ptr(), weight.data_ptr<float>(),
+                                           (int)weight.numel(), n, (int)width, (int)group, (float)eps, (float)factor,
+                                           x_ptr, x_stride, (int)gate_off, dtype_code(out, "out"), stream_of(in)),
+               "group_norm_gate");
+}
+
+void rotary_prep(const Tensor& x, const Tensor& positions, const OptTensor& slots, const Tensor& freq, Tensor& q_out,
+                 const OptTensor& k_cache, const OptTensor& v_cache, int64_t num_heads, int64_t num_kv_heads,
+                 int64_t head_dim, int64_t v_dim, int64_t rotary_dims, int64_t layout, double factor,
+                 bool value_from_key, bool value_norm, double eps, const OptTensor& status) {
+  check_cuda(x, "x");
+  check_cuda(q_out, "q_out");
+  check_same(x, q_out, "x", "q_out");
+  AKV_CHECK(num_heads > 0 && num_kv_heads > 0 && head_dim > 0 && v_dim > 0, "rotary_prep: sizes must be positive");
+  AKV_CHECK(rotary_dims >= 0 && rotary_dims % 2 == 0 && rotary_dims <= head_dim && (layout == 0 || layout == 1),
+            "rotary_prep: rotary_dims must be even and at most the head's width; layout 0 or 1");
+  AKV_CHECK(!value_from_key || v_dim == head_dim, "rotary_prep: a value that is its key has the key's width");
+  const int64_t width = (num_heads + num_kv_heads) * head_dim + (value_from_key ? 0 : num_kv_heads * v_dim);
+  AKV_CHECK(x.dim() == 2 && x.size(1) == width, "x must be [tokens, ", width, "]: the q, k (and v) columns");
+  const int64_t n = x.size(0);
+  check_i32(positions, "positions", n);
+  check_f32(freq, "freq", rotary_dims / 2);
+  AKV_CHECK(q_out.numel() == n * num_heads * head_dim, "q_out must be [tokens, heads * head_dim]");
+  akv::RotaryPrepParams p{};
+  p.x = x.data_ptr();
+  p.x_stride = width;
+  p.positions = positions.data_ptr<int>();
+  p.freq = freq.data_ptr<float>();
+  p.q_out = q_out.data_ptr();
+  if (slots.has_value()) {
+    check_i32(*slots, "slots", n);
+    p.slots = slots->data_ptr<int>();
+  }
+  if (k_cache.has_value()) {
+    AKV_CHECK(v_cache.has_value() && slots.has_value(), "k_cache needs v_cache and slots");
+    check_pages(*k_cache, "k_cache", num_kv_heads, head_dim, x);
+    check_pages(*v_cache, "v_cache", num_kv_heads, v_dim, x);
+    AKV_CHECK(k_cache->size(0) == v_cache->size(0) && k_cache->size(2) == v_cache->size(2),
+              "k_cache and v_cache must have the same pages and page size");
+    p.k_cache = k_cache->data_ptr();
+    p.v_cache = v_cache->data_ptr();
+    p.page_size = (int)k_cache->size(2);
+    p.num_pages = k_cache->size(0);
+    p.k_row_stride = k_cache->size(3);
+    p.v_row_stride = v_cache->size(3);
+  }
+  p.num_tokens = n;
+  p.num_heads = (int)num_heads;
+  p.num_kv_heads = (int)num_kv_heads;
+  p.head_dim = (int)head_dim;
+  p.v_dim = (int)v_dim;
+  p.rotary_dims = (int)rotary_dims;
+  p.layout = (int)layout;
+  p.factor = (float)factor;
+  p.value_from_key = value_from_key ? 1 : 0;
+  p.value_norm = value_norm ? 1 : 0;
+  p.eps = (float)eps;
+  p.dtype = dtype_code(x, "x");
+  p.status = status_ptr(status);
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_rotary_prep(p, stream_of(x)), "rotary_prep");
+}
+
+void pair_rows_add(Tensor& hidden, const Tensor& ids, const OptTensor& sampled, const Tensor& positions,
+                   const Tensor& cu_q, const Tensor& state_slots, Tensor& last_token, const Tensor& table,
+                   int64_t vocab, int64_t buckets, int64_t mul_prev, int64_t mul_cur) {
+  check_cuda(table, "table");
+  AKV_CHECK(table.dim() == 2 && table.size(0) == buckets + 1 && buckets >= 1, "table must be [buckets + 1, hidden]");
+  const int64_t n = ids.numel(), h = table.size(1);
+  check_i32(ids, "ids");
+  check_f32(hidden, "hidden", n * h);
+  check_i32(positions, "positions", n);
+  check_i32(cu_q, "cu_q");
+  const int64_t seqs = cu_q.numel() - 1;
+  AKV_CHECK(seqs >= 1, "cu_q must hold at least one sequence");
+  check_i32(state_slots, "state_slots", seqs);
+  AKV_CHECK(last_token.is_cuda() && last_token.scalar_type() == at::kInt && last_token.dim() == 2 &&
+            last_token.size(1) >= 1, "last_token must be int32 [slots, at least 1]");
+  akv::PairRowsParams p{};
+  p.ids = ids.data_ptr<int>();
+  if (sampled.has_value()) {
+    check_i32(*sampled, "sampled");
+    p.sampled = sampled->data_ptr<int>();
+    p.num_sampled = sampled->numel();
+  }
+  p.positions = positions.data_ptr<int>();
+  p.cu_q = cu_q.data_ptr<int>();
+  p.state_slots = state_slots.data_ptr<int>();
+  p.last_token = last_token.data_ptr<int>();
+  p.state_stride = last_token.stride(0);
+  p.table = table.data_ptr();
+  p.hidden = hidden.data_ptr<float>();
+  p.num_tokens = n;
+  p.hidden_size = h;
+  p.vocab = vocab;
+  p.buckets = buckets;
+  p.mul_prev = mul_prev;
+  p.mul_cur = mul_cur;
+  p.num_seqs = (int)seqs;
+  p.dtype = dtype_code(table, "table");
+  c10::cuda::CUDAGuard guard(table.device());
+  check_launch(akv::launch_pair_rows_add(p, stream_of(table)), "pair_rows_add");
+}
+
+void stream_add(Tensor& hidden, const Tensor& other) {
+  check_f32(hidden, "hidden");
+  check_f32(other, "other", hidden.numel());
+  c10::cuda::CUDAGuard guard(hidden.device());
+  check_launch(akv::launch_stream_add(hidden.data_ptr<float>(), other.data_ptr<float>(), hidden.numel(),
+                                      stream_of(hidden)), "stream_add");
+}
+
+void scaled_sum(const Tensor& a, const Tensor& b, Tensor& out, double sa, double sb) {
+  check_cuda(a, "a");
+  check_cuda(b, "b");
+  check_cuda(out, "out");
+  check_same(a, b, "a", "b");
+  check_same(a, out, "a", "out");
+  AKV_CHECK(a.numel() == b.numel() && a.numel() == out.numel(), "a, b and out must have the same size");
+  c10::cuda::CUDAGuard guard(a.device());
+  check_launch(akv::launch_scaled_sum(a.data_ptr(), b.data_ptr(), out.data_ptr(), (float)sa, (float)sb, a.numel(),
+                                      dtype_code(a, "a"), stream_of(a)), "scaled_sum");
+}
+
 void moe_route(const Tensor& logits, const OptTensor& correction, Tensor& chosen, Tensor& weights, int64_t groups,
                int64_t keep_groups, int64_t group_top, double scale, double weight_eps) {
   check_cuda(logits, "logits");
@@ -1380,7 +1593,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("tile_nq"), py::arg("partials"), py::arg("num_tiles"), py::arg("q_tile"), py::arg("num_splits"),
         py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("v_dim"), py::arg("window"), py::arg("chunk"),
         py::arg("scale"), py::arg("softcap"), py::arg("slopes") = py::none(), py::arg("gate") = py::none(),
-        py::arg("status") = py::none(), py::arg("kernel") = 0);
+        py::arg("status") = py::none(), py::arg("kernel") = 0, py::arg("keep_first") = 0, py::arg("sigmoid_weights") = false,
+        py::arg("head_bias") = py::none(), py::arg("out_scale") = 1.0);
   m.def("head_prep", &head_prep, py::arg("x"), py::arg("slots"), py::arg("q_out"), py::arg("k_cache"),
         py::arg("v_cache"), py::arg("v_keep"), py::arg("v_other"), py::arg("blend_weight"), py::arg("gate_out"),
         py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("v_dim"), py::arg("unit_norm"),
@@ -1412,6 +1626,25 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("delta_memory_floats", [](int64_t heads, int64_t dim, int64_t v_dim) {
     return akv::delta_memory_floats((int)heads, (int)dim, (int)v_dim);
   });
+  m.def("linear_scan", &linear_scan, py::arg("x"), py::arg("state"), py::arg("cu_q"), py::arg("state_slots"),
+        py::arg("out"), py::arg("num_heads"), py::arg("head_dim"), py::arg("v_dim"), py::arg("mode"), py::arg("q_off"),
+        py::arg("k_off"), py::arg("v_off"), py::arg("gate_bias") = py::none(), py::arg("lower") = py::none(),
+        py::arg("decay") = py::none());
+  m.def("linear_scan_state_floats", [](int64_t heads, int64_t dim, int64_t v_dim) {
+    return (int64_t)akv::linear_scan_state_floats((int)heads, (int)dim, (int)v_dim);
+  });
+  m.def("group_norm_gate", &group_norm_gate, py::arg("in"), py::arg("out"), py::arg("weight"), py::arg("group"),
+        py::arg("eps"), py::arg("factor") = 1.0, py::arg("x") = py::none(), py::arg("gate_off") = 0);
+  m.def("rotary_prep", &rotary_prep, py::arg("x"), py::arg("positions"), py::arg("slots"), py::arg("freq"),
+        py::arg("q_out"), py::arg("k_cache"), py::arg("v_cache"), py::arg("num_heads"), py::arg("num_kv_heads"),
+        py::arg("head_dim"), py::arg("v_dim"), py::arg("rotary_dims"), py::arg("layout"), py::arg("factor") = 1.0,
+        py::arg("value_from_key") = false, py::arg("value_norm") = false, py::arg("eps") = 0.0,
+        py::arg("status") = py::none());
+  m.def("pair_rows_add", &pair_rows_add, py::arg("hidden"), py::arg("ids"), py::arg("sampled"), py::arg("positions"),
+        py::arg("cu_q"), py::arg("state_slots"), py::arg("last_token"), py::arg("table"), py::arg("vocab"),
+        py::arg("buckets"), py::arg("mul_prev"), py::arg("mul_cur"));
+  m.def("stream_add", &stream_add, py::arg("hidden"), py::arg("other"));
+  m.def("scaled_sum", &scaled_sum, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("sa"), py::arg("sb"));
   m.def("moe_route", &moe_route, py::arg("logits"), py::arg("correction"), py::arg("chosen"), py::arg("weights"),
         py::arg("groups"), py::arg("keep_groups"), py::arg("group_top"), py::arg("scale"), py::arg("weight_eps"));
   m.def("moe_router", &moe_router, py::arg("x"), py::arg("w"), py::arg("logits"));

@@ -233,6 +233,10 @@ struct ScoredAttentionParams {
   const float* slopes;         // [NH] or null: score <- score - slopes[h] * (query position - key position)
   int chunk;                   // > 0: a query sees only the keys of its own block of `chunk` positions
   const float* gate;           // [N, NH] or null: a head's output is multiplied by its gate
+  int keep_first;              // > 0 (with a window): the keys at positions below it stay visible behind the window
+  int sigmoid_weights;         // 1: a visible key weighs sigmoid(score + head_bias[h]); the weights are not normalised
+  const float* head_bias;      // [NH] or null (read with sigmoid_weights)
+  float out_scale;             // every output is multiplied by it (1: nothing)
 };
 int launch_scored_attention(const ScoredAttentionParams& p, cudaStream_t stream);
 // The tcgen05 prompt kernel's scored form (attention_tcgen05.cu): bfloat16 prompt tiles with keys and values of 128
@@ -383,5 +387,83 @@ constexpr int kSampleSlices = 8;
 int launch_sample(const float* logits, const float* temperature, const float* uniform, int32_t* tokens,
                   int64_t num_rows, int64_t vocab, float* part_max, int* part_arg, double* part_sum, int* tickets,
                   cudaStream_t stream);
+
+// Linear attention with a decaying matrix memory per head (linear_memory.cu): S_t = diag(a_t) S_(t-1) + k_t v_t^T,
+// o_t = S_t^T q_t, float32, from and into the requests' state slots.  x [N, x_stride] is one product's output whose
+// columns hold q (num_heads * head_dim from q_off), the gate or key columns (the same count from k_off) and v
+// (num_heads * v_dim from v_off).
+enum LinearScanMode : int {
+  kGatedWrite = 0,      // a = f, k = 1 - f, f = lower + (1 - lower) sigmoid(x_k + gate_bias); q = silu(x_q); v = x_v
+  kConstantDecay = 1,   // a = decay[head]; k = silu(x_k); q = silu(x_q); v = silu(x_v)
+};
+constexpr int kLinearScanMaxDim = 256;
+struct LinearScanParams {
+  const void* x;
+  int64_t x_stride;
+  int q_off, k_off, v_off;
+  const float* gate_bias;      // [NH * D] or null
+  const float* lower;          // [NH * D] (kGatedWrite)
+  const float* decay;          // [NH] (kConstantDecay)
+  float* state;                // [slots, state_stride]; a slot's first linear_scan_state_floats() floats are S
+  int64_t state_stride;
+  const int32_t* cu_q;         // [num_seqs + 1]
+  const int32_t* state_slots;  // [num_seqs], negative: a padded sequence, left alone
+  float* out;                  // [N, NH * DV] float32
+  int64_t num_tokens;
+  int num_seqs, num_heads, head_dim, v_dim, mode, dtype;
+};
+bool linear_scan_shape(int head_dim, int v_dim, int* rows, int* lanes);
+int64_t linear_scan_state_floats(int num_heads, int head_dim, int v_dim);
+int launch_linear_scan(const LinearScanParams& p, cudaStream_t stream);
+// out[t, c] = in[t, c] / sqrt(mean over c's group of `group` columns of in^2 + eps) * weight[c % weight_len] * factor
+// (* sigmoid(x[t, gate_off + c]) when x is given); in float32 [N, width], out in `dtype`.
+int launch_group_norm_gate(const float* in, void* out, const float* weight, int weight_len, int64_t num_tokens,
+                           int width, int group, float eps, float factor, const void* x, int64_t x_stride,
+                           int gate_off, int dtype, cudaStream_t stream);
+
+// Rotary positions on the q and k heads of one product, the value's preparation and the cache write (rotary_prep.cu).
+struct RotaryPrepParams {
+  const void* x;               // [N, x_stride]: NH * D of q, NKV * D of k, then NKV * DV of v unless value_from_key
+  int64_t x_stride;
+  const int32_t* positions;    // [N]
+  const int32_t* slots;        // [N] page * page_size + offset, negative: not stored; may be null
+  const float* freq;           // [rotary_dims / 2]
+  void* q_out;                 // [N, NH * D]
+  void* k_cache;               // [num_pages, NKV, page_size, k_row_stride] or null
+  void* v_cache;
+  int64_t num_tokens, num_pages, k_row_stride, v_row_stride;
+  int num_heads, num_kv_heads, head_dim, v_dim, page_size;
+  int rotary_dims;             // the first so many dims of a head are turned
+  int layout;                  // 0: dim i pairs with i + rotary_dims / 2; 1: dim 2i with 2i + 1
+  float factor;                // on cos and sin
+  int value_from_key;          // 1: the value is the key head before the turn
+  int value_norm;              // 1: the value head is divided by sqrt(mean(v^2) + eps)
+  float eps;
+  int dtype;
+  int* status;
+};
+int launch_rotary_prep(const RotaryPrepParams& p, cudaStream_t stream);
+
+// hidden[t] += table[(previous token * mul_prev + token * mul_cur) mod buckets] (row `buckets` at position 0); the
+// token before a step's first row comes from, and the step's last token goes to, last_token[slot * state_stride]
+// (stream_ops.cu).
+struct PairRowsParams {
+  const int32_t* ids;          // [N]; -(r + 1) stands for sampled[r]
+  const int32_t* sampled;
+  int64_t num_sampled;
+  const int32_t* positions;    // [N]
+  const int32_t* cu_q;         // [num_seqs + 1]
+  const int32_t* state_slots;  // [num_seqs]
+  int32_t* last_token;
+  int64_t state_stride;        // int32 elements between two slots
+  const void* table;           // [buckets + 1, hidden]
+  float* hidden;               // [N, hidden]
+  int64_t num_tokens, hidden_size, vocab, buckets, mul_prev, mul_cur;
+  int num_seqs, dtype;
+};
+int launch_pair_rows_add(const PairRowsParams& p, cudaStream_t stream);
+int launch_stream_add(float* hidden, const float* other, int64_t n, cudaStream_t stream);
+int launch_scaled_sum(const void* a, const void* b, void* out, float sa, float sb, int64_t n, int dtype,
+                      cudaStream_t stream);
 
 }  // namespace akv

@@ -5,8 +5,10 @@
 //   score(i, j) = q_i . k_j * scale
 //   cap  > 0:     score <- cap * tanh(score / cap)
 //   slopes:       score <- score - slopes[h] * (i - j)            (a bias that grows with the distance)
-//   visible(i,j): j <= i, j > i - window (window > 0), floor(j / chunk) == floor(i / chunk) (chunk > 0)
-//   out_i = softmax over the visible j of score(i, j) applied to v_j, times gate[i, h] (if given)
+//   visible(i,j): j <= i, j > i - window (window > 0), floor(j / chunk) == floor(i / chunk) (chunk > 0);
+//                 with keep_first > 0 the keys j < keep_first stay visible behind a window (at their true positions)
+//   out_i = softmax over the visible j of score(i, j) applied to v_j, times gate[i, h] (if given), times out_scale
+//   sigmoid_weights: the weight of a visible key is sigmoid(score + head_bias[h]) instead, not normalised over keys
 //
 // Keys are rows of `head_dim` elements, values rows of `v_dim`; both live in paged storage
 // [pages, kv heads, page size, row stride] whose row strides are given, so a value may be a
@@ -73,7 +75,7 @@ scored_attention_kernel(ScoredAttentionParams sp, int row_groups, int64_t total_
   __syncwarp();
 
   int pos[R], first_key[R];
-  float slope[R];
+  float slope[R], bias[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const bool live = r < nrows;
@@ -83,14 +85,20 @@ scored_attention_kernel(ScoredAttentionParams sp, int row_groups, int64_t total_
     if (live && sp.chunk > 0) first = max(first, pos[r] / sp.chunk * sp.chunk);
     first_key[r] = first;
     slope[r] = (live && sp.slopes != nullptr) ? sp.slopes[kvh * G + (row0 + r) % G] : 0.f;
+    bias[r] = (live && sp.head_bias != nullptr) ? sp.head_bias[kvh * G + (row0 + r) % G] : 0.f;
   }
   const int pos_last = tile_pos + (row0 + nrows - 1) / G;
   const int lo_item = first_key[0];        // rows are in position order: the first row's first key is the lowest
   const int hi_item = pos_last + 1;
-  int per = (max(hi_item - lo_item, 0) + p.num_splits - 1) / p.num_splits;
+  // The keys this item walks are [0, kept) and [lo_item, hi_item): the first keys a window keeps, then the window.
+  // They are numbered in one run ("walk index" w: key = w below kept, lo_item + w - kept from there on), which the
+  // splits cut; without kept keys the walk index is the key less lo_item.
+  const int kept = min(sp.keep_first, lo_item);
+  int per = (max(hi_item - lo_item, 0) + kept + p.num_splits - 1) / p.num_splits;
   per = (per + 31) & ~31;
-  const int start = lo_item + split * per;
-  const int end = min(hi_item, start + per);
+  const int start = split * per;
+  const int end = min(hi_item - lo_item + kept, start + per);
+  const int jump = lo_item - kept;          // added to a walk index from `kept` on
   const float inv_cap = sp.softcap > 0.f ? 1.f / sp.softcap : 0.f;
 
   float m[R], l[R], acc[R][DC];
@@ -107,8 +115,9 @@ scored_attention_kernel(ScoredAttentionParams sp, int row_groups, int64_t total_
   const int32_t* table = p.block_table + (int64_t)seq * p.table_width;
 
   for (int kb = start; kb < end; kb += 32) {
-    const int key = kb + lane;
-    bool kvalid = key < end;
+    const int walk = kb + lane;
+    const int key = walk < kept ? walk : walk + jump;
+    bool kvalid = walk < end;
     int page = 0;
     if (kvalid) {
       const int logical = key / P;
@@ -148,10 +157,16 @@ scored_attention_kernel(ScoredAttentionParams sp, int row_groups, int64_t total_
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      const bool visible = kvalid && key <= pos[r] && key >= first_key[r];
+      const bool visible = kvalid && key <= pos[r] && (key >= first_key[r] || key < sp.keep_first);
       float sr = s[r];
       if (sp.softcap > 0.f) sr = sp.softcap * tanhf(sr * inv_cap);
       sr -= slope[r] * (float)(pos[r] - key);
+      if (sp.sigmoid_weights) {
+        // no softmax: every visible key weighs sigmoid(score + bias of the head), whatever the other keys do
+        const float pr = visible ? 1.f / (1.f + expf(-(sr + bias[r]))) : 0.f;
+        ps[r * 32 + lane] = pr;
+        continue;
+      }
       sr = visible ? sr : -CUDART_INF_F;
       const float m_new = fmaxf(m[r], warp_max(sr));
       const float alpha = (m_new == -CUDART_INF_F) ? 1.f : expf(m[r] - m_new);
@@ -166,7 +181,7 @@ scored_attention_kernel(ScoredAttentionParams sp, int row_groups, int64_t total_
     const int nk = min(32, end - kb);
     for (int j = 0; j < nk; ++j) {
       const int pj = __shfl_sync(0xffffffffu, page, j);
-      const int offj = (kb + j) % P;
+      const int offj = __shfl_sync(0xffffffffu, off, j);
       const T* vptr = v_cache + (((int64_t)pj * NKV + kvh) * P + offj) * sp.v_row_stride;
       float vv[DC];
 #pragma unroll
@@ -194,8 +209,9 @@ scored_attention_kernel(ScoredAttentionParams sp, int row_groups, int64_t total_
     const int64_t row = token * NH + head;
     if (p.num_splits == 1) {
       T* o = (T*)p.out + row * (int64_t)DV;
-      float inv = total > 0.f ? 1.f / total : 0.f;
+      float inv = sp.sigmoid_weights ? 1.f : (total > 0.f ? 1.f / total : 0.f);
       if (sp.gate != nullptr) inv *= sp.gate[row];
+      inv *= sp.out_scale;
 #pragma unroll
       for (int c = 0; c < DC; ++c) {
         const int d = c * 32 + lane;
@@ -224,7 +240,7 @@ template <typename T>
 __global__ void scored_merge_kernel(const float* __restrict__ partials, T* __restrict__ out,
                                     const int32_t* __restrict__ tile_q0, const int32_t* __restrict__ tile_nq,
                                     const float* __restrict__ gate, int q_tile, int num_heads, int num_splits,
-                                    int v_dim) {
+                                    int v_dim, int plain_sum, float out_scale) {
   __shared__ float weight[kMergeSplits];
   __shared__ float scale_out;
   pdl_launch_dependents();
@@ -236,7 +252,11 @@ __global__ void scored_merge_kernel(const float* __restrict__ partials, T* __res
   if (r >= tile_nq[tile]) return;
   const int64_t row = ((int64_t)tile_q0[tile] + r) * num_heads + head;
   const float* base = partials + row * num_splits * (int64_t)(v_dim + 2);
-  if (threadIdx.x < 32) {
+  if (plain_sum) {
+    // weights that were never normalised over the keys: the splits' sums are added as they are
+    for (int s = threadIdx.x; s < num_splits; s += blockDim.x) weight[s] = 1.f;
+    if (threadIdx.x == 0) scale_out = (gate != nullptr ? gate[row] : 1.f) * out_scale;
+  } else if (threadIdx.x < 32) {
     // one warp: the maximum over the splits, each split's weight, the weighted sum of the row sums in split order
     float ms[(kMergeSplits + 31) / 32], ls[(kMergeSplits + 31) / 32];
     float m = -CUDART_INF_F;
@@ -262,7 +282,7 @@ __global__ void scored_merge_kernel(const float* __restrict__ partials, T* __res
     if (threadIdx.x == 0) {
       float den = 0.f;
       for (int s = 0; s < num_splits; ++s) den += weight[s] * base[(int64_t)s * (v_dim + 2) + v_dim + 1];
-      scale_out = den > 0.f ? (gate != nullptr ? gate[row] : 1.f) / den : 0.f;
+      scale_out = den > 0.f ? (gate != nullptr ? gate[row] : 1.f) * out_scale / den : 0.f;
     }
   }
   __syncthreads();
@@ -285,7 +305,7 @@ static int launch_scored_merge(const ScoredAttentionParams& sp, cudaStream_t str
   const int threads = sp.v_dim <= 32 ? 32 : (sp.v_dim <= 64 ? 64 : 128);
   return (int)launch_chain(scored_merge_kernel<T>, dim3((unsigned)merge_blocks), dim3(threads), 0, stream, dim3(1, 1, 1),
                            (const float*)p.partials, (T*)p.out, p.tile_q0, p.tile_nq, sp.gate, p.q_tile, p.num_heads,
-                           p.num_splits, sp.v_dim);
+                           p.num_splits, sp.v_dim, sp.sigmoid_weights, sp.out_scale);
 }
 
 template <typename T, int DC, int R>
@@ -335,8 +355,13 @@ int launch_scored_attention(const ScoredAttentionParams& sp, cudaStream_t stream
   if (p.num_tiles == 0 || p.num_tokens == 0) return 0;
   if (p.head_dim < 1 || sp.v_dim < 1 || sp.v_dim > 512 || p.num_heads % p.num_kv_heads || p.num_splits < 1 ||
       p.num_splits > kMergeSplits ||
-      sp.k_row_stride < p.head_dim || sp.v_row_stride < sp.v_dim || sp.chunk < 0 || sp.softcap < 0.f)
+      sp.k_row_stride < p.head_dim || sp.v_row_stride < sp.v_dim || sp.chunk < 0 || sp.softcap < 0.f ||
+      sp.keep_first < 0 || (sp.keep_first > 0 && (p.window <= 0 || sp.chunk > 0)))
     return (int)cudaErrorInvalidValue;
+  // kept first keys, weights without a softmax and an output factor are the general kernel's alone
+  const bool general_only = sp.keep_first > 0 || sp.sigmoid_weights || sp.head_bias != nullptr || sp.out_scale != 1.f;
+  if (general_only)
+    return p.dtype == kBFloat16 ? launch_scored_typed<__nv_bfloat16>(sp, stream) : launch_scored_typed<float>(sp, stream);
   if (p.kernel != 1 && p.q_tile > 1 && attention_tcgen05_scored_supported(sp))
     return launch_attention_tcgen05_scored(sp, stream);
   if (p.kernel != 1 && p.q_tile == 1 && attention_tc_scored_supported(sp)) return launch_attention_tc_scored(sp, stream);

@@ -366,11 +366,14 @@ def choose_splits_shared_rows(num_tiles: int, num_kv_heads: int, rows_per_tile: 
 
 def scored_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq, *, num_tiles,
                      q_tile, num_splits, num_heads, num_kv_heads, v_dim, scale, window=0, chunk=0, softcap=0.0,
-                     slopes=None, gate=None, partials=None, status=None, out=None, kernel: str = "auto"):
+                     slopes=None, gate=None, partials=None, status=None, out=None, kernel: str = "auto",
+                     keep_first: int = 0, sigmoid_weights: bool = False, head_bias=None, out_scale: float = 1.0):
     """Causal attention of the batch's new tokens over paged keys and values of different widths, with the score
     reshaped before the softmax: ``softcap * tanh(score / softcap)`` (``softcap`` > 0), less ``slopes[h]`` times the
     distance to the key (``slopes`` float32 [heads]); a query sees the last ``window`` keys (``window`` > 0) of its own
-    block of ``chunk`` positions (``chunk`` > 0); ``gate`` (float32 [tokens, heads]) scales each head's output.
+    block of ``chunk`` positions (``chunk`` > 0), and with ``keep_first`` the keys at positions below it behind the
+    window too; ``gate`` (float32 [tokens, heads]) scales each head's output and ``out_scale`` all of them.  With
+    ``sigmoid_weights`` there is no softmax: a visible key weighs ``sigmoid(score + head_bias[h])``.
     ``k_cache`` / ``v_cache``: [pages, kv heads, page size, width]; they may be one tensor whose rows are read whole
     as keys and in their first ``v_dim`` elements as values.  Returns [tokens, heads * v_dim]; only the rows of the
     given tiles are written.  ``kernel``: ``"auto"`` takes the tensor-core kernels where they fit
@@ -383,7 +386,8 @@ def scored_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq,
     ext().scored_attention(q, k_cache, v_cache, out, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq, partials,
                            num_tiles, q_tile, num_splits, num_heads, num_kv_heads, int(v_dim), int(window or 0),
                            int(chunk or 0), float(scale), float(softcap or 0.0), slopes, gate, status,
-                           {"auto": 0, "general": 1}[kernel])
+                           {"auto": 0, "general": 1}[kernel], int(keep_first or 0), bool(sigmoid_weights), head_bias,
+                           float(out_scale))
     _launched(2 if num_splits > 1 else 1)
     return out
 
@@ -907,3 +911,119 @@ class StreamNorm:
         """Launch what is queued and run the norm kernel after all."""
         self.pending.launch()
         return add_rmsnorm(self.pending.hidden, None, self.weight, self.eps, self.dtype, status=self.pending.status)
+
+
+# ----------------------------------------------------------------------------- the stream, again
+
+def stream_add(hidden: torch.Tensor, other: torch.Tensor, delta=None):
+    """``hidden += other`` in place (both float32 [tokens, width]).  ``delta`` is what a block left pending for the
+    stream; what is still pending afterwards is handed back: a plain branch output stays pending, products that are
+    queued are launched first, and a record of sums that the stream held before (``Summed``, ``Mirrored``) is
+    dropped, since it no longer describes the stream."""
+    if isinstance(delta, PendingPhases):
+        delta.launch()
+        delta = None
+    elif isinstance(delta, (Summed, Mirrored)):
+        delta = None
+    ext().stream_add(hidden, other)
+    _launched()
+    return delta
+
+
+def scaled_sum(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float) -> torch.Tensor:
+    """``a * sa + b * sb`` of two branch outputs, formed in float32 and rounded once to their dtype."""
+    out = torch.empty_like(a)
+    ext().scaled_sum(a, b, out, float(sa), float(sb))
+    _launched()
+    return out
+
+
+def pair_rows_add(hidden, ids, positions, cu_q, state_slots, last_token, table, *, vocab, buckets, mul_prev, mul_cur,
+                  sampled=None) -> torch.Tensor:
+    """``hidden[t] += table[(previous token * mul_prev + token * mul_cur) mod buckets]``, and ``table[buckets]`` for a
+    token at position 0.  The token before a step's first row is read from ``last_token[slot, 0]`` (int32
+    [slots, >= 1]), where the step's last token of every sequence is left for the next step."""
+    ext().pair_rows_add(hidden, ids, sampled, positions, cu_q, state_slots, last_token, table, int(vocab), int(buckets),
+                        int(mul_prev), int(mul_cur))
+    _launched()
+    return hidden
+
+
+# ----------------------------------------------------------------------------- rotary positions before attention
+
+ROTARY_LAYOUTS = {"half": 0, "pairs": 1}
+
+
+def rotary_prep(x, positions, slots, freq, k_cache, v_cache, *, num_heads, num_kv_heads, head_dim, v_dim, rotary_dims,
+                layout: str, factor: float = 1.0, value_from_key: bool = False, value_norm: bool = False,
+                eps: float = 0.0, status=None) -> torch.Tensor:
+    """From one product ``x`` [tokens, q heads | k heads (| v heads)]: the first ``rotary_dims`` dims of every q and k
+    head turned by ``positions[t] * freq[i]`` (``layout`` ``"half"``: dim i pairs with i + rotary_dims / 2;
+    ``"pairs"``: dim 2i with 2i + 1; cos and sin times ``factor``); the value is the v head (divided by its root mean
+    square with ``value_norm``), or with ``value_from_key`` the k head before the turn (no v columns then); k and v go
+    to their cache slots.  Returns q [tokens, heads * head_dim]."""
+    q_out = torch.empty((x.shape[0], num_heads * head_dim), dtype=x.dtype, device=x.device)
+    ext().rotary_prep(x, positions, slots, freq, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim, v_dim,
+                      int(rotary_dims), ROTARY_LAYOUTS[layout], float(factor), bool(value_from_key), bool(value_norm),
+                      float(eps), status)
+    _launched()
+    return q_out
+
+
+# ----------------------------------------------------------------------------- linear attention with a decaying memory
+
+LINEAR_SCAN_MAX_DIM = 256
+LINEAR_SCAN_MODES = {"gated_write": 0, "constant_decay": 1}
+_SCAN_COLUMNS = 32
+
+
+def linear_scan_shape(head_dim: int, v_dim: int) -> tuple[int, int] | None:
+    """(rows of a value column per lane, lanes per column) of the scan kernel, or None when it does not take the
+    sizes."""
+    if not (0 < head_dim <= LINEAR_SCAN_MAX_DIM and 0 < v_dim <= LINEAR_SCAN_MAX_DIM):
+        return None
+    rows, lanes = (16 if head_dim <= 128 else 32), 1
+    while lanes * rows < head_dim:
+        lanes *= 2
+    return (rows, lanes) if lanes <= 8 else None
+
+
+def linear_scan_state_floats(num_heads: int, head_dim: int, v_dim: int) -> int:
+    """Floats of a request's memory (all heads) as the scan kernel lays it out: the key width padded to lanes times
+    rows per lane, the value width to slices of 32 columns."""
+    rows, lanes = linear_scan_shape(head_dim, v_dim)
+    return num_heads * ((v_dim + _SCAN_COLUMNS - 1) // _SCAN_COLUMNS) * _SCAN_COLUMNS * rows * lanes
+
+
+def linear_scan_memory(state_row: torch.Tensor, num_heads: int, head_dim: int, v_dim: int) -> torch.Tensor:
+    """One request's memory ``[heads, head_dim, v_dim]`` read out of its state row (the kernel keeps it in an order of
+    its own: [head][slice of 32 columns][row in lane][column][lane])."""
+    rows, lanes = linear_scan_shape(head_dim, v_dim)
+    slices = (v_dim + _SCAN_COLUMNS - 1) // _SCAN_COLUMNS
+    s = state_row[: num_heads * slices * _SCAN_COLUMNS * rows * lanes].view(num_heads, slices, rows, _SCAN_COLUMNS, lanes)
+    s = s.permute(0, 4, 2, 1, 3).reshape(num_heads, lanes * rows, slices * _SCAN_COLUMNS)
+    return s[:, :head_dim, :v_dim]
+
+
+def linear_scan(x, state, cu_q, state_slots, *, num_heads, head_dim, v_dim, mode: str, q_off: int, k_off: int,
+                v_off: int, gate_bias=None, lower=None, decay=None) -> torch.Tensor:
+    """``S_t = diag(a_t) S_(t-1) + k_t v_t^T; o_t = S_t^T q_t`` per head over the step's tokens, sequence by sequence,
+    from and into ``state`` [slots, floats] float32 (:func:`linear_scan_state_floats` of them per slot).  The columns
+    of ``x`` from ``q_off`` / ``k_off`` / ``v_off`` hold a product's q, gate-or-key and v.  ``mode`` ``"gated_write"``:
+    ``a = f, k = 1 - f`` with ``f = lower + (1 - lower) sigmoid(x_k + gate_bias)``, ``q = silu(x_q)``, ``v = x_v``;
+    ``"constant_decay"``: ``a = decay[head]``, q, k and v through SiLU.  Returns float32 [tokens, heads * v_dim]."""
+    out = torch.empty((x.shape[0], num_heads * v_dim), dtype=torch.float32, device=x.device)
+    ext().linear_scan(x, state, cu_q, state_slots, out, num_heads, head_dim, v_dim, LINEAR_SCAN_MODES[mode], int(q_off),
+                      int(k_off), int(v_off), gate_bias, lower, decay)
+    _launched()
+    return out
+
+
+def group_norm_gate(o, weight, *, group: int, eps: float, out_dtype, factor: float = 1.0, x=None, gate_off: int = 0):
+    """``o / sqrt(mean over each group of `group` columns of o^2 + eps) * weight * factor`` (``weight`` holds a
+    group's or the whole width's entries), times ``sigmoid(x[:, gate_off + column])`` when ``x`` is given; ``o``
+    float32 [tokens, width], the result in ``out_dtype``."""
+    out = torch.empty(o.shape, dtype=out_dtype, device=o.device)
+    ext().group_norm_gate(o, out, weight, int(group), float(eps), float(factor), x, int(gate_off))
+    _launched()
+    return out

@@ -14,7 +14,8 @@ import torch
 from ..config.spec import ModelSpec
 from ..kernels import ops
 from ..parts import (attention, block, embedding, feed_forward, gated_delta, latent_attention,  # noqa: F401
-                     norm, position, routed_experts, scored_attention)                          # (importing them registers the built-in kinds)
+                     linear_memory, norm, parallel, position, rotary_attention, routed_experts,
+                     scored_attention)                          # (importing them registers the built-in kinds)
 from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, Block, CacheSpec, ParamSpec, build_part
 
 
@@ -81,8 +82,13 @@ class DecoderModel:
     # ------------------------------------------------------------------ cache needs
 
     def cache_specs(self) -> list[CacheSpec]:
-        """One per schedule position."""
-        return [self.blocks[e.layer].cache_spec() for e in self.spec.schedule]
+        """One per schedule position, and behind them one for the embedding if it keeps something per request (the
+        cache manager treats it as one more position without pages)."""
+        specs = [self.blocks[e.layer].cache_spec() for e in self.spec.schedule]
+        own = self.embedding.cache_spec()
+        if own.kind != "none":
+            raise ValueError("an embedding keeps a state per request at most, no pages")
+        return specs + [own] if own.state_shape else specs
 
     def q_tile(self) -> int:
         """Query tokens per attention tile of the batch layout: what every mixer with a preference asks for, if they
@@ -92,7 +98,8 @@ class DecoderModel:
         return wishes.pop() if len(wishes) == 1 else ops.ATTENTION_Q_TILE
 
     def cache_of(self) -> list[int | None]:
-        return [e.cache_of for e in self.spec.schedule]
+        own = [None] if self.embedding.cache_spec().state_shape else []
+        return [e.cache_of for e in self.spec.schedule] + own
 
     # ------------------------------------------------------------------ forward
 
@@ -102,9 +109,17 @@ class DecoderModel:
         ops.stream_begin_step(self.device)
         if getattr(ctx, "shared", None):
             ctx.shared.clear()
-        hidden = self.embedding.forward(ctx.token_ids, ctx)
+        positions = len(self.spec.schedule)
+        if len(cache_views) > positions:
+            hidden = self.embedding.forward(ctx.token_ids, ctx, cache=cache_views[positions])
+        else:
+            hidden = self.embedding.forward(ctx.token_ids, ctx)
+        # a schedule that sends the stream through layers again adds the embedding's output before each such pass
+        start = hidden.clone() if any(e.add_embedding for e in self.spec.schedule) else None
         delta = None
         for pos, entry in enumerate(self.spec.schedule):
+            if entry.add_embedding:
+                delta = ops.stream_add(hidden, start, delta)
             hidden, delta = self.blocks[entry.layer].forward(hidden, delta, ctx, cache_views[pos])
         if ctx.num_logit_rows == 0:
             return None

@@ -54,7 +54,9 @@ class CacheSpec:
     ``kind``: ``"none"``, ``"full"`` (every position is kept), ``"window"`` (only the last
     ``window`` positions are ever read, pages behind it are given back) or ``"chunk"`` (a position reads only
     positions of its own block of ``chunk`` positions, counted from the start of the sequence; pages wholly before
-    the block of the next position are given back).  What a position stores
+    the block of the next position are given back).  A window cache with ``keep_first`` > 0 also keeps the pages of the
+    sequence's first ``keep_first`` positions for as long as the request lives (keys that stay visible behind the
+    window).  What a position stores
     is a tuple of named tensors (``tensors``); when none is given it is what attention stores:
     ``k`` and ``v``, each ``num_kv_heads`` rows of ``head_dim``.  A mixer that keeps one
     compressed tensor per token, or keys and values of different widths, names them itself.
@@ -70,6 +72,7 @@ class CacheSpec:
     state_shape: tuple[int, ...] = ()
     tensors: tuple[CacheTensor, ...] | None = None
     chunk: int | None = None
+    keep_first: int = 0
 
     def stored(self) -> tuple[CacheTensor, ...]:
         if self.kind == "none":
@@ -79,7 +82,7 @@ class CacheSpec:
         return (CacheTensor("k", self.num_kv_heads, self.head_dim), CacheTensor("v", self.num_kv_heads, self.head_dim))
 
     def group_key(self) -> tuple:
-        return (self.kind, self.stored(), self.window, self.chunk)
+        return (self.kind, self.stored(), self.window, self.chunk, self.keep_first)
 
 
 class Part:
@@ -181,6 +184,11 @@ class FeedForward(Part):
 
 class Embedding(Part):
     """Token ids to the float32 residual stream."""
+
+    def cache_spec(self) -> CacheSpec:
+        """What the embedding keeps per request between steps (a state only; default nothing).  When it asks for
+        state, ``forward`` is handed the view of it as the keyword ``cache``."""
+        return CacheSpec()
 
     def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
         """[tokens] int32 -> [tokens, hidden] float32.  ``ctx.sampled`` may stand for ids the host has not read."""

@@ -10,14 +10,18 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import NORMS, Embedding, Head, ParamSpec, build_part, register_embedding, register_head
+from .base import NORMS, CacheSpec, Embedding, Head, ParamSpec, build_part, register_embedding, register_head
 
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Embedding):
     """params: ``vocab_size``, ``tensor`` (the matrix's name under the prefix, default ``weight``), ``scale`` (the
     row is multiplied by it, default 1), ``position_tensor`` and ``max_positions`` (a learned table
-    [max_positions, hidden] whose row of the token's position is added, unscaled; default none)."""
+    [max_positions, hidden] whose row of the token's position is added, unscaled; default none), ``pair_table`` (None,
+    or ``tensor``, ``buckets``, ``mul_prev``, ``mul_cur``: a table [buckets + 1, hidden] whose row
+    ``(previous token * mul_prev + token * mul_cur) mod buckets`` is added, unscaled, and its last row for a
+    sequence's first token; the previous token of a step's first row is kept per request, as a state of one int32
+    that the cache manager holds with the request's state slot)."""
 
     graph_safe = True
 
@@ -31,25 +35,48 @@ class TokenEmbedding(Embedding):
         self.max_positions = int(spec.params.get("max_positions") or 0)
         if self.position_tensor is not None and self.max_positions <= 0:
             raise ValueError("token_embedding: a position table needs 'max_positions'")
+        self.pair_table = spec.params.get("pair_table")
+        if self.pair_table is not None:
+            self.pair_tensor = str(self.pair_table["tensor"])
+            self.buckets, self.mul_prev, self.mul_cur = (int(self.pair_table[k]) for k in ("buckets", "mul_prev", "mul_cur"))
+            if self.buckets <= 0:
+                raise ValueError("token_embedding: a pair table needs a positive number of buckets")
         self.weight: torch.Tensor | None = None
         self.position_rows: torch.Tensor | None = None
+        self.pair_rows: torch.Tensor | None = None
 
     def param_specs(self):
         specs = {self.tensor: ParamSpec((self.vocab_size, self.hidden_size))}
         if self.position_tensor is not None:
             specs[str(self.position_tensor)] = ParamSpec((self.max_positions, self.hidden_size))
+        if self.pair_table is not None:
+            specs[self.pair_tensor] = ParamSpec((self.buckets + 1, self.hidden_size))
         return specs
+
+    def cache_spec(self) -> CacheSpec:
+        # the request's newest token, as the bits of one float32 state entry
+        return CacheSpec(kind="none", state_shape=(1,)) if self.pair_table is not None else CacheSpec()
 
     def load(self, tensors):
         self.weight = tensors[self.tensor].contiguous()
         if self.position_tensor is not None:
             self.position_rows = tensors[str(self.position_tensor)].contiguous()
+        if self.pair_table is not None:
+            self.pair_rows = tensors[self.pair_tensor].contiguous()
 
-    def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
-        return ops.embedding(token_ids, self.weight, status=getattr(ctx, "status", None),
-                             sampled=getattr(ctx, "sampled", None), scale=self.scale,
-                             positions=ctx.positions if self.position_rows is not None else None,
-                             position_rows=self.position_rows)
+    def forward(self, token_ids: torch.Tensor, ctx, cache=None) -> torch.Tensor:
+        hidden = ops.embedding(token_ids, self.weight, status=getattr(ctx, "status", None),
+                               sampled=getattr(ctx, "sampled", None), scale=self.scale,
+                               positions=ctx.positions if self.position_rows is not None else None,
+                               position_rows=self.position_rows)
+        if self.pair_rows is None:
+            return hidden
+        if cache is None or cache.state is None:
+            raise ValueError("token_embedding: a pair table needs the request's state (its previous token)")
+        return ops.pair_rows_add(hidden, token_ids, ctx.positions, ctx.cu_q, ctx.state_slots,
+                                 cache.state.view(torch.int32), self.pair_rows, vocab=self.vocab_size,
+                                 buckets=self.buckets, mul_prev=self.mul_prev, mul_cur=self.mul_cur,
+                                 sampled=getattr(ctx, "sampled", None))
 
 
 @register_embedding("normed_token_embedding")
@@ -65,8 +92,8 @@ class NormedTokenEmbedding(TokenEmbedding):
     def children(self):
         return (self.norm,)
 
-    def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
-        rows = super().forward(token_ids, ctx)
+    def forward(self, token_ids: torch.Tensor, ctx, cache=None) -> torch.Tensor:
+        rows = super().forward(token_ids, ctx, cache)
         # the norm part, asked for float32 activations, hands back the stream itself
         return self.norm.forward(rows, None, ctx)
 

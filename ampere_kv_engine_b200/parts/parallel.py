@@ -1,0 +1,103 @@
+"""Two mixers side by side: both read the same input, and the layer's branch is ``left_scale * left(x) +
+right_scale * right(x)``.
+
+Each side is a registered mixer kind of its own.  The layer has one cache view, so at most one side keeps pages; a
+side that keeps a state gets its share of the position's state (the sides' floats lie one behind the other in a
+request's slot).  When both sides offer ``heads_forward`` / ``out_projection`` (everything before the output
+projection, with an ``out_scale`` applied in float32 before the one rounding) and neither output projection has a
+bias, the two output projections run as one product over the sides' outputs laid next to each other; otherwise each
+side runs whole and ``ops.scaled_sum`` adds them up (sides with a bias on their output projection, or kinds that do
+not offer the two methods).
+"""
+
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from ..config.spec import PartSpec
+from ..kernels import ops
+from .base import MIXERS, CacheSpec, Mixer, build_part, register_mixer
+
+
+@register_mixer("parallel")
+class ParallelMixers(Mixer):
+    """params: ``left`` and ``right`` (PartSpecs of registered mixer kinds), ``left_scale``, ``right_scale``."""
+
+    adds_residual = True
+
+    def __init__(self, spec, **kw):
+        super().__init__(spec, **kw)
+        p = spec.params
+        self.scales = (float(p.get("left_scale", 1.0)), float(p.get("right_scale", 1.0)))
+        sides = []
+        for side, scale in zip((p["left"], p["right"]), self.scales):
+            if not isinstance(side, PartSpec):
+                raise ValueError("parallel: 'left' and 'right' are part specs of mixers")
+            sides.append(side)
+        built = [build_part(MIXERS, side, hidden_size=self.hidden_size, dtype=self.dtype, device=self.device)
+                 for side in sides]
+        # one product for both output projections, if both sides can hand over what stands before theirs
+        self.joined = all(hasattr(m, "heads_forward") and hasattr(m, "out_projection")
+                          and not getattr(m, "out_bias", False) for m in built)
+        if self.joined:
+            built = [build_part(MIXERS, PartSpec(side.kind, dict(side.params, out_scale=scale), side.prefix),
+                                hidden_size=self.hidden_size, dtype=self.dtype, device=self.device)
+                     for side, scale in zip(sides, self.scales)]
+        self.sides = tuple(built)
+        specs = [m.cache_spec() for m in self.sides]
+        paged = [s for s in specs if s.kind != "none"]
+        if len(paged) > 1:
+            raise ValueError("parallel: only one side may keep pages (a schedule position has one cache)")
+        self.state_sizes = []
+        for s in specs:
+            if len(s.state_shape) > 1:
+                raise ValueError("parallel: a side's state must be a flat run of floats")
+            self.state_sizes.append(int(s.state_shape[0]) if s.state_shape else 0)
+        base = paged[0] if paged else CacheSpec()
+        total = sum(self.state_sizes)
+        self._cache_spec = dataclasses.replace(base, state_shape=(total,) if total else ())
+        self.w_o = None
+
+    @property
+    def graph_safe(self):
+        return all(m.graph_safe for m in self.sides)
+
+    def children(self):
+        return self.sides
+
+    def preferred_q_tile(self):
+        wishes = {m.preferred_q_tile() for m in self.sides} - {None}
+        return wishes.pop() if len(wishes) == 1 else None
+
+    def cache_spec(self) -> CacheSpec:
+        return self._cache_spec
+
+    def load(self, tensors):
+        """The sides have their tensors by now (children load first is not promised, so the joined matrix is made at
+        the first step)."""
+
+    def _views(self, cache):
+        views, at = [], 0
+        for size in self.state_sizes:
+            state = None
+            if size:
+                state = cache.state[:, at:at + size]
+                at += size
+            views.append(dataclasses.replace(cache, state=state))
+        return views
+
+    def forward(self, x, ctx, cache, residual=None):
+        left, right = self.sides
+        cl, cr = self._views(cache)
+        if self.joined:
+            if self.w_o is None:
+                self.w_o = torch.cat((left.out_projection()[0], right.out_projection()[0]), dim=1).contiguous()
+            both = torch.cat((left.heads_forward(x, ctx, cl), right.heads_forward(x, ctx, cr)), dim=1)
+            if residual is not None:
+                summed = ops.linear_into_residual(both, self.w_o, residual, status=ctx.status)
+                if summed is not None:
+                    return summed
+            return ops.linear(both, self.w_o, partial_ok=True, status=ctx.status)
+        return ops.scaled_sum(left.forward(x, ctx, cl), right.forward(x, ctx, cr), *self.scales)

@@ -161,7 +161,8 @@ class ScoredAttention(Mixer):
 
 
 def run_attention(ctx, group, q, k_cache, v_cache, out, *, num_heads, num_kv_heads, v_dim, scale, window=0, chunk=0,
-                  softcap=0.0, slopes=None, gate=None, plain=False) -> None:
+                  softcap=0.0, slopes=None, gate=None, plain=False, keep_first=0, sigmoid_weights=False, head_bias=None,
+                  out_scale=1.0) -> None:
     """``ops.scored_attention`` over the step's tiles: the single-token tiles of a mixed step (they come first) apart
     from the prompt tiles, each with the number of key splits that fills the GPU.  ``plain``: nothing is done to the
     scores and the plain kernels take the sizes: ``ops.paged_attention`` runs instead."""
@@ -173,7 +174,7 @@ def run_attention(ctx, group, q, k_cache, v_cache, out, *, num_heads, num_kv_hea
         if hi <= lo:
             continue
         longest, mean = ctx.decode_contexts if q_tile == 1 else (ctx.max_context, ctx.max_context)
-        for limit in (window, chunk):
+        for limit in (window + keep_first if window else 0, chunk):
             if limit:
                 longest, mean = min(longest, limit), min(mean, limit)
         if plain:
@@ -184,9 +185,10 @@ def run_attention(ctx, group, q, k_cache, v_cache, out, *, num_heads, num_kv_hea
                 ctx.tile_nq[lo:hi], num_tiles=hi - lo, q_tile=q_tile, num_splits=splits, num_heads=num_heads,
                 num_kv_heads=num_kv_heads, window=window, scale=scale, status=ctx.status, out=out)
             continue
-        tensor_core = k_cache is not v_cache and ops.scored_takes_tensor_cores(
+        general_only = bool(keep_first or sigmoid_weights or head_bias is not None or out_scale != 1.0)
+        tensor_core = not general_only and k_cache is not v_cache and ops.scored_takes_tensor_cores(
             q.dtype, q.shape[1] // num_heads, v_dim, group_size, k_cache.shape[2], prompt=q_tile > 1)
-        if k_cache is v_cache and ops.shared_rows_take_tensor_cores(q.dtype, q.shape[1] // num_heads, v_dim):
+        if not general_only and k_cache is v_cache and ops.shared_rows_take_tensor_cores(q.dtype, q.shape[1] // num_heads, v_dim):
             splits = ops.choose_splits_shared_rows(hi - lo, num_kv_heads, q_tile * group_size, longest)
         elif q_tile > 1 and tensor_core:
             splits = 1
@@ -197,4 +199,5 @@ def run_attention(ctx, group, q, k_cache, v_cache, out, *, num_heads, num_kv_hea
             q, k_cache, v_cache, group.block_table, ctx.cu_q, ctx.ctx_lens, ctx.tile_seq[lo:hi], ctx.tile_q0[lo:hi],
             ctx.tile_nq[lo:hi], num_tiles=hi - lo, q_tile=q_tile, num_splits=splits, num_heads=num_heads,
             num_kv_heads=num_kv_heads, v_dim=v_dim, scale=scale, window=window, chunk=chunk, softcap=softcap,
-            slopes=slopes, gate=gate, status=ctx.status, out=out)
+            slopes=slopes, gate=gate, status=ctx.status, out=out, keep_first=keep_first,
+            sigmoid_weights=sigmoid_weights, head_bias=head_bias, out_scale=out_scale)

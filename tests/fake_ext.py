@@ -186,7 +186,8 @@ class FakeExt:
 
     def scored_attention(self, q, k_cache, v_cache, out, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq,
                          partials, num_tiles, q_tile, num_splits, num_heads, num_kv_heads, v_dim, window, chunk, scale,
-                         softcap, slopes=None, gate=None, status=None, kernel=0):
+                         softcap, slopes=None, gate=None, status=None, kernel=0, keep_first=0, sigmoid_weights=False,
+                         head_bias=None, out_scale=1.0):
         page_size = k_cache.shape[2]
         d = q.shape[1] // num_heads
         group = num_heads // num_kv_heads
@@ -205,6 +206,8 @@ class FakeExt:
             if chunk:
                 lo = max(lo, first_pos // chunk * chunk)
             keys = torch.arange(lo, ctx)
+            if keep_first and lo > 0:
+                keys = torch.cat((torch.arange(0, min(keep_first, lo)), keys))
             pages = block_table[s].long()[keys // page_size]
             assert (pages >= 0).all(), "attention would read a page that is not held"
             k = k_cache[pages, :, keys % page_size][..., :d].float()
@@ -217,14 +220,19 @@ class FakeExt:
                 scores = scores - slopes.float()[:, None, None] * (pos - keys[None, :]).float()[None]
             visible = keys[None, :] <= pos
             if window:
-                visible &= keys[None, :] > pos - window
+                visible &= (keys[None, :] > pos - window) | (keys[None, :] < keep_first)
             if chunk:
                 visible &= (keys[None, :] // chunk) == (pos // chunk)
-            scores = scores.masked_fill(~visible[None], -math.inf)
-            o = torch.einsum("hts,shd->thd", torch.softmax(scores, -1), v.repeat_interleave(group, dim=1))
+            if sigmoid_weights:
+                if head_bias is not None:
+                    scores = scores + head_bias.float()[:, None, None]
+                weights = torch.sigmoid(scores) * visible[None]
+            else:
+                weights = torch.softmax(scores.masked_fill(~visible[None], -math.inf), -1)
+            o = torch.einsum("hts,shd->thd", weights, v.repeat_interleave(group, dim=1))
             if gate is not None:
                 o = o * gate[q0:q1].float()[:, :, None]
-            out[q0:q1] = o.reshape(n, -1).to(out.dtype)
+            out[q0:q1] = (o * out_scale).reshape(n, -1).to(out.dtype)
 
     def head_prep(self, x, slots, q_out, k_cache, v_cache, v_keep, v_other, blend_weight, gate_out, num_heads,
                   num_kv_heads, head_dim, v_dim, unit_norm, eps, status=None, q_weight=None, k_weight=None,
@@ -360,6 +368,106 @@ class FakeExt:
                 before = state[slot, memory:memory + (taps - 1) * channels].view(taps - 1, channels)
                 stream = torch.cat((before, x[q0:q1, :channels].float()), dim=0)
                 state[slot, memory:memory + (taps - 1) * channels] = stream[-(taps - 1):].reshape(-1)
+
+    # ------------------------------------------------------------------ rotary positions, linear memories, the stream
+
+    def rotary_prep(self, x, positions, slots, freq, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim, v_dim,
+                    rotary_dims, layout, factor=1.0, value_from_key=False, value_norm=False, eps=0.0, status=None):
+        n = x.shape[0]
+        xf = x.float()
+        a, b = num_heads * head_dim, num_kv_heads * head_dim
+        q, k = xf[:, :a].view(n, num_heads, head_dim), xf[:, a:a + b].view(n, num_kv_heads, head_dim)
+        angle = positions.float()[:, None] * freq.float()[None, :]
+        cos, sin = (torch.cos(angle) * factor)[:, None, :], (torch.sin(angle) * factor)[:, None, :]
+
+        def turn(t):
+            out = t.clone()
+            if layout == 0:
+                u, v = t[..., :rotary_dims // 2], t[..., rotary_dims // 2:rotary_dims]
+                out[..., :rotary_dims // 2] = u * cos - v * sin
+                out[..., rotary_dims // 2:rotary_dims] = v * cos + u * sin
+            else:
+                u, v = t[..., 0:rotary_dims:2], t[..., 1:rotary_dims:2]
+                out[..., 0:rotary_dims:2] = u * cos - v * sin
+                out[..., 1:rotary_dims:2] = v * cos + u * sin
+            return out
+
+        q_out.copy_(turn(q).reshape(n, -1).to(q_out.dtype))
+        if k_cache is None or slots is None:
+            return
+        if value_from_key:
+            v = k
+        else:
+            v = xf[:, a + b:].view(n, num_kv_heads, v_dim)
+            if value_norm:
+                v = v * torch.rsqrt(v.square().mean(-1, keepdim=True) + eps)
+        page_size = k_cache.shape[2]
+        keep = slots >= 0
+        s = slots[keep].long()
+        k_cache[s // page_size, :, s % page_size] = turn(k)[keep].to(k_cache.dtype)
+        v_cache[s // page_size, :, s % page_size] = v[keep].to(v_cache.dtype)
+
+    def linear_scan_state_floats(self, heads, dim, v_dim):
+        from ampere_kv_engine_b200.kernels import ops
+        return ops.linear_scan_state_floats(heads, dim, v_dim)
+
+    def linear_scan(self, x, state, cu_q, state_slots, out, num_heads, head_dim, v_dim, mode, q_off, k_off, v_off,
+                    gate_bias=None, lower=None, decay=None):
+        H, D, V = num_heads, head_dim, v_dim
+        cu, slots = cu_q.tolist(), state_slots.tolist()
+        xf = x.float()
+        silu = torch.nn.functional.silu
+        for s, slot in enumerate(slots):
+            q0, q1 = cu[s], cu[s + 1]
+            if slot < 0 or q1 <= q0:
+                continue
+            S = state[slot, :H * D * V].view(H, D, V).clone()       # the stand-in keeps S in plain order
+            for t in range(q0, q1):
+                q = silu(xf[t, q_off:q_off + H * D]).view(H, D)
+                raw = xf[t, k_off:k_off + H * D]
+                v = xf[t, v_off:v_off + H * V].view(H, V)
+                if mode == 0:
+                    f = lower + (1 - lower) * torch.sigmoid(raw + (gate_bias if gate_bias is not None else 0))
+                    a, k = f.view(H, D), (1 - f).view(H, D)
+                else:
+                    a, k, v = decay[:, None].expand(H, D), silu(raw).view(H, D), silu(v)
+                S = a[:, :, None] * S + k[:, :, None] * v[:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1)
+            state[slot, :H * D * V] = S.reshape(-1)
+
+    def group_norm_gate(self, o, out, weight, group, eps, factor=1.0, x=None, gate_off=0):
+        n, width = o.shape
+        y = o.view(n, width // group, group)
+        y = y * torch.rsqrt(y.square().mean(-1, keepdim=True) + eps)
+        y = y.reshape(n, width) * weight.repeat(width // weight.numel()) * factor
+        if x is not None:
+            y = y * torch.sigmoid(x[:, gate_off:gate_off + width].float())
+        out.copy_(y.to(out.dtype))
+
+    def pair_rows_add(self, hidden, ids, sampled, positions, cu_q, state_slots, last_token, table, vocab, buckets,
+                      mul_prev, mul_cur):
+        ids = ids.long()
+        if sampled is not None:
+            ids = torch.where(ids < 0, sampled.long()[(-ids - 1).clamp(min=0)], ids)
+        cu, slots = cu_q.tolist(), state_slots.tolist()
+        for s, slot in enumerate(slots):
+            q0, q1 = cu[s], cu[s + 1]
+            if q1 <= q0:
+                continue
+            prev = torch.empty(q1 - q0, dtype=torch.long)
+            prev[0] = int(last_token[slot, 0]) if slot >= 0 else 0
+            prev[1:] = ids[q0:q1 - 1]
+            rows = (prev * mul_prev + ids[q0:q1] * mul_cur) % buckets
+            rows = torch.where(positions[q0:q1].long() > 0, rows, torch.full_like(rows, buckets))
+            hidden[q0:q1] += table[rows].float()
+            if slot >= 0:
+                last_token[slot, 0] = int(ids[q1 - 1])
+
+    def stream_add(self, hidden, other):
+        hidden += other
+
+    def scaled_sum(self, a, b, out, sa, sb):
+        out.copy_((a.float() * sa + b.float() * sb).to(out.dtype))
 
     # ------------------------------------------------------------------ routed experts
 
