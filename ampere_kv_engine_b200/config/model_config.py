@@ -514,7 +514,7 @@ class RenadraConfig:
         return self.vocab
 
     @staticmethod
-    def _check_rot(m: dict, where: str, dim: int, scaling: bool) -> None:
+    def _check_rot(m: dict, where: str, dim: int) -> None:
         rot = _section(m, "rot", where)
         where_r = where + "rot: "
         dims = _sized(rot, "dims", where_r)
@@ -523,8 +523,6 @@ class RenadraConfig:
         if dims % 2 or dims > dim:
             raise ConfigError(f"config.json: {where_r}'dims' must be even and at most 'dim' ({dim}), got {dims}")
         if rot.get("scaling") is not None:
-            if not scaling:
-                raise ConfigError(f"config.json: {where_r}'scaling' is not part of this mixer")
             s = _section(rot, "scaling", where_r)
             for key in ("factor", "original", "fast", "slow"):
                 if _number(s, key, where_r + "scaling: ") <= 0:
@@ -538,20 +536,17 @@ class RenadraConfig:
             raise ConfigError(f"config.json: {where}'heads' ({m['heads']}) must be a multiple of 'kv_heads' "
                               f"({m['kv_heads']})")
         _number(m, "scale", where)
-        cls._check_rot(m, where, m["dim"], scaling=left)
+        cls._check_rot(m, where, m["dim"])
         mask = _section(m, "mask", where)
         _sized(mask, "size", where + "mask: ")
-        if left:
-            if m["vdim"] != m["dim"]:
-                raise ConfigError(f"config.json: {where}'vdim' ({m['vdim']}) must equal 'dim' ({m['dim']}): the values "
-                                  f"are the keys")
-            keep = mask.get("keep_first", 0)
-            if isinstance(keep, bool) or not isinstance(keep, int) or keep < 0:
-                raise ConfigError(f"config.json: {where}mask: 'keep_first' must be a non-negative integer, got {keep!r}")
-            if _number(m, "softcap", where) <= 0:
-                raise ConfigError(f"config.json: {where}'softcap' must be positive")
-        elif mask.get("keep_first"):
-            raise ConfigError(f"config.json: {where}mask: 'keep_first' is not part of this mixer")
+        keep = mask.get("keep_first") or 0
+        if isinstance(keep, bool) or not isinstance(keep, int) or keep < 0:
+            raise ConfigError(f"config.json: {where}mask: 'keep_first' must be a non-negative integer, got {keep!r}")
+        if m.get("softcap") is not None and _number(m, "softcap", where) <= 0:
+            raise ConfigError(f"config.json: {where}'softcap' must be positive")
+        if left and m["vdim"] != m["dim"]:
+            raise ConfigError(f"config.json: {where}'vdim' ({m['vdim']}) must equal 'dim' ({m['dim']}): the values "
+                              f"are the keys")
 
     @staticmethod
     def _check_memory(m: dict, where: str, decay: bool) -> None:

@@ -36,7 +36,8 @@ def _attention(config: RenadraConfig, m: dict, prefix: str) -> PartSpec:
     return PartSpec("rotary_attention", {
         "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"], "v_dim": m["vdim"],
         "scale": m["scale"], "position_encoding": _rope(m["rot"], "pairs"), "bias": ("q", "k", "v", "out"),
-        "bias_suffix": ".b", "value_norm": True, "norm_eps": config.norm_eps, "window": m["mask"]["size"],
+        "bias_suffix": ".b", "value_norm": True, "norm_eps": config.norm_eps, "softcap": m.get("softcap"),
+        "window": m["mask"]["size"], "keep_first": m["mask"].get("keep_first") or 0,
         "names": {"q": "q", "k": "k", "v": "v", "out": "o"}}, prefix)
 
 
@@ -44,8 +45,8 @@ def _left(m: dict, prefix: str) -> PartSpec:
     return PartSpec("rotary_attention", {
         "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"], "v_dim": m["vdim"],
         "scale": m["scale"], "position_encoding": _rope(m["rot"], "half"), "bias": ("q", "k"), "bias_suffix": ".b",
-        "value_from_key": True, "softcap": m["softcap"], "window": m["mask"]["size"],
-        "keep_first": m["mask"].get("keep_first", 0), "weights": "sigmoid", "head_bias": True,
+        "value_from_key": True, "softcap": m.get("softcap"), "window": m["mask"]["size"],
+        "keep_first": m["mask"].get("keep_first") or 0, "weights": "sigmoid", "head_bias": True,
         "names": {"q": "q", "k": "k", "out": "o", "head_bias": "pb"}}, prefix)
 
 
