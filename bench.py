@@ -1,6 +1,6 @@
 """Benchmark of the engine on one B200: decode tokens per second at the Qwen3-8B shape.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference] [--shape 8b|14b|32b|sukalorn|zifuzen]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference] [--shape 8b|14b|32b|sukalorn|zifuzen|renadra]
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch through the engine's own step
 function (every kernel of the model and the token choice); ``value`` is batch / step time, timed with CUDA
@@ -10,6 +10,8 @@ chosen tokens back.  ``prefill`` is one 2,048-token prompt in one step; ``points
 and 64; ``roofline`` compares the bytes a decode step must read (every weight once, the live requests'
 cache) with the copy bandwidth.  Weights are random (seeded), token ids synthetic (seeded uniform).
 ``--shape zifuzen`` does for the Zifuzen design what ``--shape sukalorn`` does for Sukalorn.
+``--shape renadra`` sets four Renadra layers beside Zifuzen layers of equal size with dense feed-forwards, and
+Renadra's kernels alone beside the like kernels of the other designs.
 ``--shape sukalorn`` prints a line of its own: prefill and decode of four Sukalorn layers at two sizes beside Qwen3
 layers of equal size, and the attention kernels alone.
 Between timed steps nothing is flushed: every step streams the whole model (16 GB at full depth) through
@@ -517,6 +519,45 @@ def zifuzen_config(z: dict, layers: int) -> dict:
             "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": out}
 
 
+# Renadra at sizes that resemble a real model's layers: four layers (hgrn2, attention behind a window, a rotary
+# attention with kept first keys and sigmoid weights beside a lightning attention, hgrn2), all with dense feed-forwards,
+# beside Zifuzen layers of the same width, heads, head size and feed-forward width (delta rule, attention, delta rule,
+# attention; dense feed-forwards): the package's other design with a float32 memory per request and head.
+RENADRA_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, memory_heads=16, window=1024, keep=64),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, memory_heads=32, window=1024, keep=64),
+}
+
+
+def renadra_config(z: dict, layers: int) -> dict:
+    d = z["dim"]
+    rot = {"base": 1000000.0, "dims": d}
+    memory = {"heads": z["memory_heads"], "dim": d, "vdim": d}
+    attention = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5,
+                 "mask": {"size": z["window"]}, "rot": dict(rot)}
+    left = dict(attention, softcap=30.0, mask={"size": z["window"], "keep_first": z["keep"]},
+                rot=dict(rot, scaling={"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}))
+    right = dict(memory, decay=[1.0 - 2.0 ** -(2 + 8 * h / max(1, z["memory_heads"] - 1)) for h in range(z["memory_heads"])])
+    parallel = {"left": left, "right": right, "left_scale": 0.8, "right_scale": 1.1}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    pattern = [("hgrn2", memory), ("attention", attention), ("parallel", parallel), ("hgrn2", memory)]
+    return {"architecture": "Renadra", "vocab": SUKALORN_VOCAB, "width": z["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 100003, "mul_prev": 1000003, "mul_cur": 31}},
+            "layers": [{"type": pattern[i % 4][0], "mixer": json.loads(json.dumps(pattern[i % 4][1])), "mlp": dict(mlp)}
+                       for i in range(layers)]}
+
+
+def zifuzen_dense_like(z: dict, layers: int) -> dict:
+    attention = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                 "scale": z["dim"] ** -0.5}
+    delta = {"heads": z["memory_heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "conv": 4}
+    pattern = [("delta", delta), ("attention", attention), ("delta_2", delta), ("attention", attention)]
+    return {"architecture": "Zifuzen", "vocab": SUKALORN_VOCAB, "width": z["width"], "max_positions": CONTEXT,
+            "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "layers": [{"type": pattern[i % 4][0], "mixer": dict(pattern[i % 4][1]),
+                        "mlp": {"kind": "dense", "ff": z["ff"]}} for i in range(layers)]}
+
+
 def sukalorn_shape(args, design: str = "sukalorn") -> int:
     """Prefill (one 2,048-token prompt) and decode (batch 8 from 1,024-token prompts) of the Sukalorn design at two
     layer sizes, each beside Qwen3 layers of the same width, heads, head size and feed-forward width, through the
@@ -602,6 +643,25 @@ def sukalorn_shape(args, design: str = "sukalorn") -> int:
                 "launches_per_decode_step": launches, "matrix_bytes": weights,
                 "decode_hbm_frac_weights_only": round(weights / (decode_ms / 1000) / 1e9 / peaks["hbm_gbs"], 4)}
 
+    def layout(seq_q, q_tile):
+        """Batch layout tensors of sequences given as (context, new tokens): (keyword arguments of the attention ops,
+        pages used, tokens)."""
+        page = args.page_size
+        cu, tiles = [0], []
+        for s, (_, n) in enumerate(seq_q):
+            tiles += [(s, cu[-1] + t0, min(q_tile, n - t0)) for t0 in range(0, n, q_tile)]
+            cu.append(cu[-1] + n)
+        pages_per = [(c + page - 1) // page for c, _ in seq_q]
+        table = torch.full((len(seq_q), max(pages_per)), -1, dtype=torch.int32)
+        at = 0
+        for s, n in enumerate(pages_per):
+            table[s, :n] = torch.arange(at, at + n, dtype=torch.int32)
+            at += n
+        dev = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+        return dict(block_table=table.to(device), cu_q=dev(cu), ctx_lens=dev([c for c, _ in seq_q]),
+                    tile_seq=dev([t[0] for t in tiles]), tile_q0=dev([t[1] for t in tiles]),
+                    tile_nq=dev([t[2] for t in tiles]), num_tiles=len(tiles), q_tile=q_tile), at, cu[-1]
+
     def kernels_alone(z: dict) -> dict:
         """The attention kernels by themselves at this size: a 2,048-token prompt as one sequence, and single tokens
         of `batch` sequences that each hold 1,024 keys."""
@@ -610,22 +670,6 @@ def sukalorn_shape(args, design: str = "sukalorn") -> int:
         row = z["kv_rank"] + z["rot_dim"]
         bf = dict(dtype=torch.bfloat16, device=device)
         g = torch.Generator(device=device).manual_seed(1)
-
-        def layout(seq_q, q_tile):
-            cu, tiles = [0], []
-            for s, (_, n) in enumerate(seq_q):
-                tiles += [(s, cu[-1] + t0, min(q_tile, n - t0)) for t0 in range(0, n, q_tile)]
-                cu.append(cu[-1] + n)
-            pages_per = [(c + page - 1) // page for c, _ in seq_q]
-            table = torch.full((len(seq_q), max(pages_per)), -1, dtype=torch.int32)
-            at = 0
-            for s, n in enumerate(pages_per):
-                table[s, :n] = torch.arange(at, at + n, dtype=torch.int32)
-                at += n
-            dev = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
-            return dict(block_table=table.to(device), cu_q=dev(cu), ctx_lens=dev([c for c, _ in seq_q]),
-                        tile_seq=dev([t[0] for t in tiles]), tile_q0=dev([t[1] for t in tiles]),
-                        tile_nq=dev([t[2] for t in tiles]), num_tiles=len(tiles), q_tile=q_tile), at, cu[-1]
 
         for name, seq_q, q_tile in (("prompt", [(PREFILL_TOKENS, PREFILL_TOKENS)], ops.ATTENTION_Q_TILE),
                                     ("decode", [(PROMPT_LEN, 1)] * batch, 1)):
@@ -746,7 +790,153 @@ def sukalorn_shape(args, design: str = "sukalorn") -> int:
                     "frac_of_bf16_peak": round(flops / (ms / 1000) / 1e12 / peaks["bf16_tflops"], 4)}
         return out
 
+    def renadra_kernels_alone(z: dict) -> dict:
+        """Renadra's own kernels by themselves at this size, each beside the like kernel of another design: the
+        linear-memory scan in both modes beside the delta rule's scan (all walk a float32 memory per head token by
+        token), the norm behind it, the rotary preparation, and the attention with kept first keys and sigmoid weights
+        beside the capped, sloped and gated softmax attention of the Sukalorn design and the plain attention behind a
+        window.  A 2,048-token prompt as one sequence, and single tokens of `batch` sequences that hold 1,024 keys."""
+        out = {}
+        H, D, V = z["memory_heads"], z["dim"], z["dim"]
+        heads, kvh, dim, page = z["heads"], z["kv_heads"], z["dim"], args.page_size
+        window, keep = z["window"], z["keep"]
+        g = torch.Generator(device=device).manual_seed(3)
+        dev = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+        fp32_peak = peaks.get("fp32_tflops") or FP32_FMA_TFLOPS
+        bf = dict(dtype=torch.bfloat16, device=device)
+        floats = ops.linear_scan_state_floats(H, D, V)
+        taps = 4
+        delta_memory, delta_floats = ops.delta_state_floats(H, kvh, D, V, taps)
+        state = torch.zeros((batch + 1, max(floats, delta_floats)), device=device)
+        lower = torch.rand((H * D,), device=device, generator=g) * 0.9
+        gate_bias = torch.zeros((H * D,), device=device)
+        decay = torch.tensor(renadra_config(z, 4)["layers"][2]["mixer"]["right"]["decay"], device=device)
+        norm_head, norm_wide = torch.ones((V,), device=device), torch.ones((H * V,), device=device)
+
+        def record(key, fn, *, flops=0.0, moved=0.0, tensor=False):
+            for _ in range(3):
+                fn()
+            ms = timed(fn, 5, flush_l2=True)
+            entry = {"ms": round(ms, 4)}
+            if flops:
+                peak = peaks["bf16_tflops"] if tensor else fp32_peak
+                entry["tflops"] = round(flops / (ms / 1000) / 1e12, 3)
+                entry["frac_of_bf16_peak" if tensor else "frac_of_fp32_fma_peak"] = round(
+                    flops / (ms / 1000) / 1e12 / peak, 4)
+            if moved:
+                entry["gbs"] = round(moved / (ms / 1000) / 1e9, 1)
+                entry["frac_of_hbm"] = round(moved / (ms / 1000) / 1e9 / peaks["hbm_gbs"], 4)
+            out[key] = entry
+
+        for name, lens in (("prompt", [PREFILL_TOKENS]), ("decode", [1] * batch)):
+            tokens = sum(lens)
+            cu, slots = dev([0] + [sum(lens[:i + 1]) for i in range(len(lens))]), dev(list(range(len(lens))))
+            # the memories: [q | f or k | v | g] columns of one product
+            x = torch.randn((tokens, 2 * H * D + 2 * H * V), device=device, generator=g).to(torch.bfloat16)
+            sizes_kw = dict(num_heads=H, head_dim=D, v_dim=V, q_off=0, k_off=H * D, v_off=2 * H * D)
+            scan_flops = 5.0 * tokens * H * D * V               # decay, write and read of every memory element
+            scan_moved = 2.0 * 4 * len(lens) * floats + 2.0 * tokens * 3 * H * D + 4.0 * tokens * H * V
+            record(f"{name}_hgrn2_scan", lambda: ops.linear_scan(x, state, cu, slots, mode="gated_write",
+                                                                 gate_bias=gate_bias, lower=lower, **sizes_kw),
+                   flops=scan_flops, moved=scan_moved)
+            record(f"{name}_lightning_scan", lambda: ops.linear_scan(x, state, cu, slots, mode="constant_decay",
+                                                                     decay=decay, **sizes_kw),
+                   flops=scan_flops, moved=scan_moved)
+            o = ops.linear_scan(x, state, cu, slots, mode="constant_decay", decay=decay, **sizes_kw)
+            record(f"{name}_norm_per_head", lambda: ops.group_norm_gate(o, norm_head, group=V, eps=1e-6,
+                                                                        out_dtype=torch.bfloat16),
+                   moved=6.0 * tokens * H * V)
+            record(f"{name}_norm_all_heads_gated", lambda: ops.group_norm_gate(
+                o, norm_wide, group=H * V, eps=1e-6, out_dtype=torch.bfloat16, x=x, gate_off=2 * H * D + H * V),
+                moved=8.0 * tokens * H * V)
+            # the like kernel: the delta rule's scan at the same heads and widths
+            channels = 2 * kvh * D + H * V
+            xd = torch.randn((tokens, channels + H * V + 2 * H), device=device, generator=g).to(torch.bfloat16)
+            conv = torch.rand((channels, taps), device=device, generator=g) - 0.3
+            delta_kw = dict(num_heads=H, num_kv_heads=kvh, head_dim=D, v_dim=V, taps=taps)
+            state.zero_()
+            qkv, coef = ops.delta_prep(xd, conv, torch.full((H,), -3.0, device=device), torch.zeros((H,), device=device),
+                                       state, cu, slots, unit_eps=1e-6, **delta_kw)
+            record(f"{name}_like_delta_scan", lambda: ops.delta_scan(qkv, coef, xd, norm_head, state, cu, slots,
+                                                                     norm_eps=1e-6, **delta_kw),
+                   flops=7.0 * tokens * H * D * V,
+                   moved=2.0 * 4 * len(lens) * delta_memory + 4.0 * tokens * (channels + 2 * H * V))
+            state.zero_()
+        for name, seq_q, q_tile in (("prompt", [(PREFILL_TOKENS, PREFILL_TOKENS)], ops.ATTENTION_Q_TILE),
+                                    ("decode", [(PROMPT_LEN, 1)] * batch, 1)):
+            lay, pages, tokens = layout(seq_q, q_tile)
+            rand = lambda *shape: torch.randn(shape, generator=g, **bf)
+            k_pages, v_pages = rand(pages, kvh, page, dim), rand(pages, kvh, page, dim)
+            q = rand(tokens, heads * dim)
+            # rotary preparation: reads the product, writes q and both cache rows
+            xp = rand(tokens, (heads + kvh) * dim)
+            positions = dev([c - n + i for c, n in seq_q for i in range(n)])
+            slot_map = dev(list(range(tokens)))
+            freq = (1000000.0 ** (-torch.arange(0, dim, 2, device=device).float() / dim)).contiguous()
+            record(f"{name}_rotary_prep", lambda: ops.rotary_prep(
+                xp, positions, slot_map, freq, k_pages, v_pages, num_heads=heads, num_kv_heads=kvh, head_dim=dim, v_dim=dim,
+                rotary_dims=dim, layout="half", factor=1.1, value_from_key=True),
+                moved=2.0 * tokens * ((heads + kvh) * dim + heads * dim + 2 * kvh * dim))
+            # (query, visible key) pairs behind the window with the kept first keys; keys a decode step reads
+            seen = lambda p: min(p + 1, window) + min(keep, max(0, p + 1 - window))
+            pairs = sum(seen(c - n + i) for c, n in seq_q for i in range(n))
+            keys = sum(seen(c - 1) for c, _ in seq_q)
+            pairs_plain = sum(min(c - n + i + 1, window) for c, n in seq_q for i in range(n))
+            keys_plain = sum(min(c, window) for c, _ in seq_q)
+            group = heads // kvh
+            head_bias = torch.zeros((heads,), device=device)
+            slopes = torch.exp2(-8.0 * torch.arange(1, heads + 1, device=device) / heads).float()
+            gate = torch.rand((tokens, heads), device=device, generator=g)
+            reach = window + keep
+            tc = ops.scored_takes_tensor_cores(torch.bfloat16, dim, dim, group, page, prompt=q_tile > 1)
+            cases = {
+                "sigmoid_kept_attention": (lambda s: ops.scored_attention(
+                    q, k_pages, v_pages, num_splits=s, num_heads=heads, num_kv_heads=kvh, v_dim=dim, scale=dim ** -0.5,
+                    softcap=30.0, window=window, keep_first=keep, sigmoid_weights=True, head_bias=head_bias,
+                    out_scale=0.8, **lay), pairs, keys,
+                    ops.choose_splits(lay["num_tiles"], kvh, q_tile * group, min(PROMPT_LEN, reach), False)),
+                "window_attention": (lambda s: ops.paged_attention(
+                    q, k_pages, v_pages, num_splits=s, num_heads=heads, num_kv_heads=kvh, window=window,
+                    scale=dim ** -0.5, **lay), pairs_plain, keys_plain,
+                    ops.choose_splits(lay["num_tiles"], kvh, q_tile * group, min(PROMPT_LEN, window), True)
+                    if q_tile == 1 else 1),
+                "like_sukalorn_attention": (lambda s: ops.scored_attention(
+                    q, k_pages, v_pages, num_splits=s, num_heads=heads, num_kv_heads=kvh, v_dim=dim, scale=dim ** -0.5,
+                    softcap=30.0, slopes=slopes, gate=gate, window=window, **lay), pairs_plain, keys_plain,
+                    1 if q_tile > 1 and tc else ops.choose_splits(lay["num_tiles"], kvh, q_tile * group,
+                                                                  min(PROMPT_LEN, window), tc)),
+            }
+            for case, (fn, n_pairs, n_keys, splits) in cases.items():
+                if name == "prompt":
+                    record(f"{name}_{case}", lambda: fn(splits), flops=4.0 * heads * dim * n_pairs, tensor=True)
+                else:
+                    record(f"{name}_{case}", lambda: fn(splits), moved=2.0 * 2 * kvh * dim * n_keys)
+                out[f"{name}_{case}"]["splits"] = splits
+        return out
+
     sizes = {}
+    if design == "renadra":
+        with ClockSampler() as clocks:
+            for name, z in RENADRA_SIZES.items():
+                sizes[name] = {"renadra": measure(renadra_config(z, layers)),
+                               "zifuzen_dense": measure(zifuzen_dense_like(z, layers)),
+                               "kernels": renadra_kernels_alone(z)}
+        head = sizes["4k"]["renadra"]
+        line = {"metric": "decode tok/s at batch 8 of four Renadra layers (width 4,096, B200); prefill, a smaller size, "
+                          "Zifuzen layers of equal size with dense feed-forwards and Renadra's kernels alone, each "
+                          "beside the like kernel of another design, alongside",
+                "value": head["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": head["decode_ms"], "higher_is_better": True, "dtype": "bf16",
+                "data": "synthetic (seeded uniform token ids, seeded random weights)",
+                "config": {"model": "Renadra", "layers": layers, "sizes": RENADRA_SIZES, "vocab": SUKALORN_VOCAB,
+                           "global_batch": batch, "prompt_len": PROMPT_LEN, "prefill_tokens": PREFILL_TOKENS,
+                           "page_size": args.page_size, "l2": "whole steps: inputs larger than L2; kernels alone: L2 "
+                           "flushed (a 256 MB write) before every timed launch", "peaks": peaks["source"],
+                           "fp32_fma_tflops": FP32_FMA_TFLOPS},
+                "gpu_launches": head["launches_per_decode_step"] * args.steps, "sizes": sizes,
+                "clocks": clocks.summary()}
+        print(json.dumps(line))
+        return 0
     if design == "zifuzen":
         with ClockSampler() as clocks:
             for name, z in ZIFUZEN_SIZES.items():
@@ -793,18 +983,18 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page (a power of two, 16 or more)")
-    parser.add_argument("--shape", choices=sorted(SHAPES) + ["sukalorn", "zifuzen"], default="8b",
+    parser.add_argument("--shape", choices=sorted(SHAPES) + ["renadra", "sukalorn", "zifuzen"], default="8b",
                         help="8b: the headline benchmark; 14b: a mixed scheduler load of 64 requests; 32b: long-context "
                              "decode at batch 16; sukalorn: prefill and decode of the Sukalorn design at two layer "
-                             "sizes beside Qwen3 layers of equal size; zifuzen: the same for the Zifuzen design (each prints "
-                             "its own one line)")
+                             "sizes beside Qwen3 layers of equal size; zifuzen: the same for the Zifuzen design; renadra: the Renadra design beside "
+                             "Zifuzen layers of equal size (each prints its own one line)")
     parser.add_argument("--layers", type=int, default=None,
                         help="run fewer layers of the same sizes (reported in config beside the full count)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
     args = parser.parse_args()
 
-    if args.shape in ("sukalorn", "zifuzen"):
+    if args.shape in ("renadra", "sukalorn", "zifuzen"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference arm runs the 8b shape only"}))
             return 0

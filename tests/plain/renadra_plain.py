@@ -70,7 +70,8 @@ def rotate(x, rot, layout):
     T = x.shape[0]
     dims = int(rot["dims"])
     freq, factor = rotary_frequencies(rot)
-    angle = torch.arange(T, dtype=torch.float64)[:, None] * freq[None, :]
+    # the design forms positions and angles in float32: one rounding of the frequency and one of the product
+    angle = (torch.arange(T, dtype=torch.float32)[:, None] * freq.float()[None, :]).double()
     cos = (torch.cos(angle) * factor).to(x.dtype)[:, None, :]
     sin = (torch.sin(angle) * factor).to(x.dtype)[:, None, :]
     out = x.clone()

@@ -152,3 +152,66 @@ def plain_logits(folder: str, raw: dict, requests: dict[str, list[int]]) -> dict
     """float64 logits of every request as a whole sequence, as float32."""
     w = plain_weights(folder)
     return {rid: plain.forward(raw, w, toks).float() for rid, toks in requests.items()}
+
+
+def random_config(seed: int) -> dict:
+    """A configuration whose every size, constant, layer order and loop is drawn from the seed: three to six layers of
+    any mixers (at least one of each family), widths and head sizes that are no multiples of 16, windows shorter and
+    longer than a page, kept first keys or none, rescaled frequencies or none, layers without a feed-forward, a pair
+    table or none, a loop or none."""
+    g = torch.Generator().manual_seed(1000 + seed)
+    pick = lambda *options: options[int(torch.randint(0, len(options), (1,), generator=g))]
+    num = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+
+    def rot(dim, scaling):
+        dims = 2 * num(1, dim // 2)
+        s = (pick(2.0, 4.0, 8.0), pick(32, 64, 256), pick(8.0, 16.0, 32.0), pick(1.0, 2.0)) if scaling else None
+        return _rot(dims, pick(100.0, 10000.0, 1000000.0), s)
+
+    def attention():
+        kv = num(1, 3)
+        dim = pick(8, 12, 16, 24, 32, 64)
+        return _attention(kv * num(1, 3), kv, dim, pick(8, 12, 16, 20, 32, dim), round(dim ** -0.5 * pick(0.8, 1.0, 1.5), 4),
+                          num(3, 80), rot(dim, False))
+
+    def left():
+        kv = num(1, 3)
+        dim = pick(8, 12, 16, 24, 32, 64)
+        return _left(kv * num(1, 3), kv, dim, round(dim ** -0.5 * pick(0.8, 1.0, 1.5), 4), num(3, 60), pick(0, 1, 7, 20),
+                     pick(5.0, 30.0, 50.0), rot(dim, pick(True, True, False)))
+
+    def memory(decay):
+        heads = num(1, 5)
+        m = _memory(heads, pick(4, 8, 12, 20, 32, 48, 64), pick(4, 8, 12, 20, 32, 40, 64))
+        if decay:
+            m["decay"] = [round(1.0 - 0.5 ** num(1, 10), 6) for _ in range(heads)]
+        return m
+
+    width = pick(24, 40, 48, 72, 96, 128)
+    kinds = ["attention", "hgrn2", "parallel"] + [pick("attention", "hgrn2", "parallel") for _ in range(num(0, 3))]
+    kinds = [kinds[i] for i in torch.randperm(len(kinds), generator=g).tolist()]
+    layers = []
+    for kind in kinds:
+        ff = pick(None, 32, 56, 64, 100)
+        if kind == "attention":
+            layers.append(_layer(kind, attention(), ff))
+        elif kind == "hgrn2":
+            layers.append(_layer(kind, memory(False), ff))
+        else:
+            layers.append(_layer(kind, {"left": left(), "right": memory(True), "left_scale": pick(0.5, 0.8, 1.0),
+                                        "right_scale": pick(0.7, 1.0, 1.2)}, ff))
+    raw = {"architecture": "Renadra", "vocab": num(50, 300), "width": width, "norm": {"eps": pick(1e-5, 1e-6)},
+           "embedding": {"scale": pick(1.0, 2.5, 9.0)}, "layers": layers}
+    if pick(True, True, False):
+        raw["embedding"]["bigram"] = {"buckets": pick(7, 61, 257), "mul_prev": num(1, 200), "mul_cur": num(1, 50)}
+    if pick(True, True, False):
+        start = num(0, len(layers) - 1)
+        raw["loop"] = {"start": start, "stop": num(start + 1, len(layers)), "times": num(2, 3)}
+    return raw
+
+
+def random_model_folder(seed: int) -> str:
+    name = f"random{seed}"
+    if name not in CONFIGS:
+        CONFIGS[name] = (random_config(seed), (8, 16, 32)[seed % 3])
+    return model_folder(name, seed=seed)

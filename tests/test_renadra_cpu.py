@@ -194,3 +194,21 @@ def test_a_model_without_a_pair_table_or_a_loop_keeps_no_embedding_state(fake_ex
     prompt = [5, 7, 11, 13, 17, 19, 23, 29, 31]
     got = engine.generate([prompt], max_new_tokens=5, ignore_eos=True)
     assert got == [plain.greedy_generate(raw, zu.plain_weights(folder), prompt, 5)]
+
+
+@pytest.mark.parametrize("seed", [1, 4, 7, 11])
+def test_random_configuration_on_the_stand_in_kernels(fake_ext, seed):
+    """Layer orders, sizes, windows, kept keys, loops and pair tables drawn from the seed, in a mixed trace whose pages
+    and state slots are used again."""
+    folder = zu.random_model_folder(seed)
+    raw, page = zu.CONFIGS[f"random{seed}"]
+    requests = ru.make_requests(raw["vocab"], (1, 2, 23, 61, 90, 37), seed=seed)
+    expected = zu.plain_logits(folder, raw, requests)
+    trace = ru.trace_mixed(requests, 64 * 5, seed=seed)
+    outputs = ru.run_inprocess(folder, "float32", trace, 64 * 5, page_size=page)
+    saved = dict(ru.TOL["float32"])
+    ru.TOL["float32"] = dict(atol=2e-4, rtol=2e-4)
+    try:
+        ru.compare(trace, outputs, expected, "float32")
+    finally:
+        ru.TOL["float32"] = saved

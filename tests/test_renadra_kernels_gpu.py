@@ -223,6 +223,7 @@ def _scan_inputs(mode, heads, dim, vdim, tokens, dtype, seed):
     g = torch.Generator().manual_seed(seed)
     width = 2 * heads * dim + heads * vdim + 7              # columns the scan does not read lie behind
     x = (2.0 * torch.randn(tokens, width, generator=g)).to(dtype)
+    g = torch.Generator().manual_seed(seed + 1000)          # gates that do not depend on the number of tokens
     extra = {}
     if mode == "gated_write":
         extra["lower"] = 1.0 - torch.logspace(-3, 0, heads * dim)[torch.randperm(heads * dim, generator=g)]
