@@ -121,11 +121,17 @@ struct FaParams {
   // the scored form of the narrow kernel (launch_attention_tcgen05_scored): the score q.k * scale goes through
   // softcap * tanh(. / softcap) (softcap > 0), loses slopes[h] * (query position - key position) (slopes given), a
   // query sees only keys of its own block of `chunk` positions (chunk > 0), and a head's output is multiplied by
-  // gate[token, head] (gate given)
+  // gate[token, head] (gate given) and all outputs by out_scale; with keep_first > 0 (and a window) the keys at
+  // positions below it stay visible behind the window; with `sigmoid` there is no softmax: a visible key weighs
+  // sigmoid(score + head_bias[h]) and the weights are not normalised
   float softcap = 0.f;
   const float* slopes = nullptr;
   int chunk = 0;
   const float* gate = nullptr;
+  int keep_first = 0;
+  int sigmoid = 0;
+  const float* head_bias = nullptr;
+  float out_scale = 1.f;
 };
 
 // Shared memory: Q [2 halves][128 rows][128 B] | K/V ring: per stage K [2][64][128 B], V [2][64][128 B] |
@@ -235,7 +241,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
   if (kScored && fp.chunk > 0) lo = max(lo, tile_pos / fp.chunk * fp.chunk);      // the first row's block of positions
   lo = lo / fp.box_rows * fp.box_rows;
   const int hi = tile_pos + nq;
-  const int num_blocks = (hi - lo + kKeys - 1) / kKeys;
+  // Kept first keys: blocks of them come first, then the walk jumps to the window's first box.  Only boxes that hold a
+  // kept key are fetched (the pages behind them may have been given back): the rows after them count as past the
+  // end.  When the window's first box follows the kept boxes directly, or lies among them, the walk is one run from
+  // key 0 and the mask does the rest.
+  int kept_blocks = 0, kept_hi = 0;
+  if (kScored && fp.keep_first > 0) {
+    kept_hi = (fp.keep_first + fp.box_rows - 1) / fp.box_rows * fp.box_rows;
+    if (lo > kept_hi) kept_blocks = (kept_hi + kKeys - 1) / kKeys;
+    else lo = 0;
+  }
+  const int num_blocks = kept_blocks + (hi - lo + kKeys - 1) / kKeys;
+  auto key0_of = [&](int b) -> int { return b < kept_blocks ? b * kKeys : lo + (b - kept_blocks) * kKeys; };
+  auto end_of = [&](int b) -> int { return b < kept_blocks ? kept_hi : hi; };       // keys of block b end before it
 
   if (tid == 0) {
     bar_init(q_full, 1);
@@ -283,8 +301,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     const int boxes = kKeys / fp.box_rows;
     const int x = lane >> 2, kind = lane & 3;
     auto row_of = [&](int blk) -> int {       // first cache row of this lane's box in block blk, -1: no box
-      const int key = lo + blk * kKeys + x * fp.box_rows;
-      if (blk >= num_blocks || x >= boxes || key >= hi) return -1;
+      const int key = key0_of(blk) + x * fp.box_rows;
+      if (blk >= num_blocks || x >= boxes || key >= end_of(blk)) return -1;
       const int logical = key / P;
       int page = logical < p.table_width ? table[logical] : -1;
       if (page < 0 || page >= p.num_pages) {
@@ -406,12 +424,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     const float scale_log2 = kScored ? 1.f : p.scale * kLog2e;
     const float slope = (kScored && fp.slopes != nullptr) ? fp.slopes[kvh * G + head_local] : 0.f;
     const int first_key = (kScored && fp.chunk > 0 && live) ? pos / fp.chunk * fp.chunk : 0;
+    const int keep = kScored ? fp.keep_first : 0;
+    const bool sigmoid = kScored && fp.sigmoid != 0;
+    // inside the sigmoid, in log2 units
+    const float head_bias = (sigmoid && fp.head_bias != nullptr) ? fp.head_bias[kvh * G + head_local] * kLog2e : 0.f;
     float m_ref = -CUDART_INF_F, l = 0.f;
 
     for (int b = 0; b < num_blocks; ++b) {
       const int s = b % kStagesKV;
-      const int key0 = lo + b * kKeys;
-      const int nvalid = min(kKeys, hi - key0);
+      const int key0 = key0_of(b);
+      const int nvalid = min(kKeys, end_of(b) - key0);
       if (ok && !bar_wait(&s_ready[b & 1], (b >> 1) & 1)) ok = false;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       uint32_t raw[2][32];
@@ -433,26 +455,29 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
           if (fp.softcap > 0.f)
             x = fp.softcap * (1.f - __fdividef(2.f, ex2(x * inv_cap * (2.f * kLog2e)) + 1.f));
           x = fmaf(-slope, (float)(pos - (key0 + j)), x);
-          raw[j >> 5][j & 31] = __float_as_uint(x * kLog2e);
+          raw[j >> 5][j & 31] = __float_as_uint(fmaf(x, kLog2e, head_bias));
         }
       }
       const bool plain = ok && nvalid == kKeys && key0 + kKeys - 1 <= tile_pos &&
-                         (p.window <= 0 || key0 > tile_pos + nq - 1 - p.window) &&
+                         (p.window <= 0 || key0 > tile_pos + nq - 1 - p.window || key0 + kKeys <= keep) &&
                          (!kScored || fp.chunk <= 0 || key0 >= (tile_pos + nq - 1) / fp.chunk * fp.chunk);
       float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
       if (plain && live) {
+        if (!sigmoid) {
 #pragma unroll
-        for (int j = 0; j < kKeys; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j >> 5][j & 31]));
+          for (int j = 0; j < kKeys; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j >> 5][j & 31]));
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < kKeys; ++j) {
           const int key = key0 + j;
-          const bool visible = ok && live && j < nvalid && key <= pos && (p.window <= 0 || key > pos - p.window) &&
-                               (!kScored || key >= first_key);
+          const bool visible = ok && live && j < nvalid && key <= pos &&
+                               (p.window <= 0 || key > pos - p.window || key < keep) && (!kScored || key >= first_key);
           if (!visible) raw[j >> 5][j & 31] = 0xff800000u;     // -inf
-          mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j >> 5][j & 31]));
+          if (!sigmoid) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j >> 5][j & 31]));
         }
       }
+      // weights that are not normed over the keys have no reference maximum: nothing is ever rescaled
       const float bmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;     // the scale is positive
       // raise the reference maximum only when it pays; then O (in TMEM) and l are rescaled
       const bool raise = bmax > m_ref + kRescaleThreshold || (m_ref == -CUDART_INF_F && bmax > -CUDART_INF_F);
@@ -489,8 +514,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
 #pragma unroll
       for (int j = 0; j < kKeys; j += 2) {
         // 2^(score * scale - m): one multiply-add; -inf stays -inf and gives 0
-        const float pa = ex2(fmaf(__uint_as_float(raw[j >> 5][j & 31]), scale_log2, -m_sub));
-        const float pb = ex2(fmaf(__uint_as_float(raw[(j + 1) >> 5][(j + 1) & 31]), scale_log2, -m_sub));
+        float pa, pb;
+        if (sigmoid) {
+          // 1 / (1 + 2^-x): -inf gives 1 / inf = 0
+          pa = __frcp_rn(1.f + ex2(-__uint_as_float(raw[j >> 5][j & 31])));
+          pb = __frcp_rn(1.f + ex2(-__uint_as_float(raw[(j + 1) >> 5][(j + 1) & 31])));
+        } else {
+          pa = ex2(fmaf(__uint_as_float(raw[j >> 5][j & 31]), scale_log2, -m_sub));
+          pb = ex2(fmaf(__uint_as_float(raw[(j + 1) >> 5][(j + 1) & 31]), scale_log2, -m_sub));
+        }
         part[(j >> 1) & 3] += pa + pb;
         __nv_bfloat162 h = __floats2bfloat162_rn(pa, pb);
         packed[j >> 1] = *reinterpret_cast<uint32_t*>(&h);
@@ -519,6 +551,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     if (num_blocks > 0 && ok && !bar_wait(&pv_done[(num_blocks - 1) & 1], ((num_blocks - 1) >> 1) & 1)) ok = false;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     float inv = (ok && l > 0.f) ? 1.f / l : 0.f;
+    if (sigmoid) inv = ok ? 1.f : 0.f;
+    if (kScored) inv *= fp.out_scale;
     if (kScored && fp.gate != nullptr && live) inv *= fp.gate[(int64_t)(q0 + token_local) * NH + kvh * G + head_local];
     __nv_bfloat16* out = (__nv_bfloat16*)p.out + ((int64_t)(q0 + token_local) * NH + kvh * G + head_local) * kD;
 #pragma unroll
@@ -1049,6 +1083,7 @@ int launch_attention_tcgen05(const PagedAttentionParams& p, cudaStream_t stream)
 
 // The scored form: keys and values of 128 dims in storage of their own, everything else as the plain kernel takes it.
 bool attention_tcgen05_scored_supported(const ScoredAttentionParams& sp) {
+  if (sp.keep_first > 0 && (sp.base.window <= 0 || sp.chunk > 0)) return false;
   return sp.v_dim == kD && sp.k_row_stride == kD && sp.v_row_stride == kD && sp.base.k_cache != sp.base.v_cache &&
          attention_tcgen05_supported(sp.base);
 }
@@ -1064,7 +1099,8 @@ int launch_attention_tcgen05_scored(const ScoredAttentionParams& sp, cudaStream_
   if (!q_map_for(p.q, p.num_tokens, p.num_heads, G, tq, &q_map) || !cache_map(p.k_cache, rows, box_rows, &k_map) ||
       !cache_map(p.v_cache, rows, box_rows, &v_map))
     return (int)cudaErrorInvalidValue;
-  FaParams fp{p, tq, subtiles, box_rows, sp.softcap, sp.slopes, sp.chunk, sp.gate};
+  FaParams fp{p, tq, subtiles, box_rows, sp.softcap, sp.slopes, sp.chunk, sp.gate,
+              sp.keep_first, sp.sigmoid_weights, sp.head_bias, sp.out_scale};
   fp.p.num_splits = 1;
   const dim3 grid((unsigned)(p.num_tiles * subtiles), (unsigned)p.num_kv_heads, 1u);
   // two CTAs per SM with two K/V stages each when there are more CTAs than SMs, else one with four stages

@@ -10,9 +10,11 @@
 //
 // Work split: a block owns (sequence, head, 32 value columns) for the whole step.  A value column of S lives in the
 // registers of `lanes` neighbouring lanes (ROWS rows each), so writing a token is thread-local and reading it out is
-// one sum over those lanes.  Tokens are staged through shared memory CHUNK at a time (activations and gates are
-// worked out once per chunk by all threads).  S moves between registers and the request's state slot in an order of
-// its own ([head][slice][row in lane][column][lane]), so that the loads and stores of a decode step are coalesced.
+// one sum over those lanes.  Tokens are staged through two shared-memory buffers CHUNK at a time: a thread loads the
+// next chunk's product columns into registers before it walks the current chunk's tokens, and turns them into
+// activations and gates and stores them afterwards, so that the loads' latency lies behind the walk and there is one
+// block barrier per chunk.  S moves between registers and the request's state slot in an order of its own
+// ([head][slice][row in lane][column][lane]), so that the loads and stores of a decode step are coalesced.
 // Tokens are walked one by one whatever the step holds: the memory after a token does not depend on how the tokens
 // were cut into steps.
 //
@@ -26,18 +28,21 @@ namespace akv {
 namespace {
 
 constexpr int kScanColumns = 32;     // value columns per block
-constexpr int kScanChunk = 16;       // tokens staged at a time
+constexpr int kScanRounds = 3;       // staged entries per thread and token: 2 * dim + 32 <= 3 * threads for every shape
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 
-template <typename T, int MODE, int ROWS>
+// floats between two lanes' rows of q (or of a) in shared memory: padded where several lanes share a column, so that
+// the float4 reads of a group's lanes fall into different banks
+__host__ __device__ constexpr int scan_pitch(int rows, int lanes) { return lanes > 1 ? rows + 4 : rows; }
+
+template <typename T, int MODE, int ROWS, int CHUNK>
 __global__ void __launch_bounds__(256)
 linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   pdl_launch_dependents();
   pdl_wait();
   const int H = p.num_heads, D = p.head_dim, DV = p.v_dim;
-  const int DP = lanes * ROWS;                         // rows of S with padding
   const int slice = blockIdx.x % slices;
   const int head = (blockIdx.x / slices) % H;
   const int seq = blockIdx.x / (slices * H);
@@ -48,11 +53,12 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   const int tid = threadIdx.x, threads = blockDim.x;
   const int sub = tid % lanes, col = tid / lanes;
   const int j = slice * kScanColumns + col;
+  const int pitch = scan_pitch(ROWS, lanes);
+  const int vec = lanes * pitch;                       // floats of a token's q (or a) in shared memory
+  const int per_token = 2 * vec + kScanColumns;        // [q | a | v]
+  const int per_buffer = CHUNK * per_token;
 
-  extern __shared__ float smem[];
-  float* qs = smem;                                    // [CHUNK][DP]
-  float* as = qs + kScanChunk * DP;                    // [CHUNK][DP]: f (gated write) or k (constant decay)
-  float* vs = as + kScanChunk * DP;                    // [CHUNK][32]
+  extern __shared__ __align__(16) float smem[];
 
   float* mem = p.state + (int64_t)slot * p.state_stride +
                ((int64_t)head * slices + slice) * ROWS * (int64_t)threads + tid;
@@ -61,61 +67,114 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   for (int r = 0; r < ROWS; ++r) S[r] = mem[(int64_t)r * threads];
   const float decay = MODE == kConstantDecay ? p.decay[head] : 0.f;
 
-  const T* x = (const T*)p.x;
-  const int wide = H * DV;
-  for (int c0 = 0; c0 < n; c0 += kScanChunk) {
-    const int nt = min(kScanChunk, n - c0);
-    for (int idx = tid; idx < nt * DP; idx += threads) {
-      const int t = idx / DP, d = idx - t * DP;
-      float qv = 0.f, av = MODE == kGatedWrite ? 1.f : 0.f;      // padded rows stay zero
-      if (d < D) {
-        const T* row = x + (int64_t)(t0 + c0 + t) * p.x_stride;
-        const int ch = head * D + d;
-        qv = silu_f(to_float<T>(row[p.q_off + ch]));
-        const float raw = to_float<T>(row[p.k_off + ch]);
+  // What a thread stages of every token: entry i = tid + round * threads of [q (D) | f or k (D) | v (the slice's
+  // columns)].  Its column of x, its place in a token's shared-memory row and its gate constants are worked out once.
+  const int mine_cols = min(kScanColumns, DV - slice * kScanColumns);
+  const int fetch_per_token = 2 * D + mine_cols;
+  const T* src[kScanRounds];
+  int dst[kScanRounds], kind[kScanRounds];             // kind 0: q, 1: f or k, 2: v
+  float low[kScanRounds], bias[kScanRounds];
+  const T* x = (const T*)p.x + (int64_t)t0 * p.x_stride;
+#pragma unroll
+  for (int r = 0; r < kScanRounds; ++r) {
+    const int i = tid + r * threads;
+    src[r] = nullptr;
+    dst[r] = kind[r] = 0;
+    low[r] = bias[r] = 0.f;
+    if (i < fetch_per_token) {
+      if (i < D) {
+        src[r] = x + p.q_off + head * D + i;
+        dst[r] = i / ROWS * pitch + i % ROWS;
+      } else if (i < 2 * D) {
+        const int d = i - D, ch = head * D + d;
+        src[r] = x + p.k_off + ch;
+        dst[r] = vec + d / ROWS * pitch + d % ROWS;
+        kind[r] = 1;
         if (MODE == kGatedWrite) {
-          const float low = p.lower[ch];
-          av = low + (1.f - low) * sigmoid_f(raw + (p.gate_bias != nullptr ? p.gate_bias[ch] : 0.f));
-        } else {
-          av = silu_f(raw);
+          low[r] = p.lower[ch];
+          bias[r] = p.gate_bias != nullptr ? p.gate_bias[ch] : 0.f;
         }
+      } else {
+        src[r] = x + p.v_off + head * DV + slice * kScanColumns + (i - 2 * D);
+        dst[r] = 2 * vec + (i - 2 * D);
+        kind[r] = 2;
       }
-      qs[idx] = qv;
-      as[idx] = av;
     }
-    for (int idx = tid; idx < nt * kScanColumns; idx += threads) {
-      const int t = idx / kScanColumns, c = idx - t * kScanColumns;
-      const int jj = slice * kScanColumns + c;
-      float vv = 0.f;
-      if (jj < DV) {
-        vv = to_float<T>(x[(int64_t)(t0 + c0 + t) * p.x_stride + p.v_off + head * DV + jj]);
-        if (MODE == kConstantDecay) vv = silu_f(vv);
+  }
+  float regs[kScanRounds][CHUNK];
+  auto fetch = [&](int first, int count) {
+#pragma unroll
+    for (int r = 0; r < kScanRounds; ++r) {
+#pragma unroll
+      for (int t = 0; t < CHUNK; ++t) {
+        regs[r][t] = 0.f;
+        if (src[r] != nullptr && t < count) regs[r][t] = to_float<T>(src[r][(int64_t)(first + t) * p.x_stride]);
       }
-      vs[idx] = vv;
     }
-    __syncthreads();
-    for (int t = 0; t < nt; ++t) {
-      const float v = vs[t * kScanColumns + col];
-      const float4* q4 = reinterpret_cast<const float4*>(qs + t * DP + sub * ROWS);
-      const float4* a4 = reinterpret_cast<const float4*>(as + t * DP + sub * ROWS);
-      float o0 = 0.f, o1 = 0.f;
+  };
+  auto stash = [&](float* buffer, int count) {
+#pragma unroll
+    for (int r = 0; r < kScanRounds; ++r) {
+      if (src[r] == nullptr) continue;
+#pragma unroll
+      for (int t = 0; t < CHUNK; ++t) {
+        if (t >= count) break;
+        const float raw = regs[r][t];
+        float y;
+        if (kind[r] == 0) y = silu_f(raw);
+        else if (kind[r] == 1) y = MODE == kGatedWrite ? low[r] + (1.f - low[r]) * sigmoid_f(raw + bias[r]) : silu_f(raw);
+        else y = MODE == kGatedWrite ? raw : silu_f(raw);
+        buffer[t * per_token + dst[r]] = y;
+      }
+    }
+  };
+  // rows of S beyond the dim never change: q and k stay zero there, a forget gate one; value columns beyond the
+  // width stay zero
+  for (int i = tid; i < 2 * per_buffer; i += threads) {
+    const int e = i % per_token;
+    smem[i] = (MODE == kGatedWrite && e >= vec && e < 2 * vec) ? 1.f : 0.f;
+  }
+  __syncthreads();
+  fetch(0, min(CHUNK, n));
+  stash(smem, min(CHUNK, n));
+  __syncthreads();
+  const int wide = H * DV;
+  for (int c0 = 0; c0 < n; c0 += CHUNK) {
+    const int count = min(CHUNK, n - c0), next = min(CHUNK, n - c0 - CHUNK);
+    const float* row = smem + ((c0 / CHUNK) & 1) * per_buffer;
+    if (next > 0) fetch(c0 + CHUNK, next);
+    float* o_row = p.out + (int64_t)(t0 + c0) * wide + head * DV + j;
+#pragma unroll 2
+    for (int t = 0; t < count; ++t, row += per_token, o_row += wide) {
+      const float v = row[2 * vec + col];
+      const float4* q4 = reinterpret_cast<const float4*>(row + sub * pitch);
+      const float4* a4 = reinterpret_cast<const float4*>(row + vec + sub * pitch);
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int r4 = 0; r4 < ROWS / 4; ++r4) {
         const float4 q = q4[r4], a = a4[r4];
-        const float qa[4] = {q.x, q.y, q.z, q.w}, aa[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int r = r4 * 4 + e;
-          if (MODE == kGatedWrite) S[r] = aa[e] * S[r] + (1.f - aa[e]) * v;
-          else S[r] = decay * S[r] + aa[e] * v;
-          if (e & 1) o1 += S[r] * qa[e];
-          else o0 += S[r] * qa[e];
+        const int r = r4 * 4;
+        if (MODE == kGatedWrite) {
+          S[r] = fmaf(1.f - a.x, v, a.x * S[r]);
+          S[r + 1] = fmaf(1.f - a.y, v, a.y * S[r + 1]);
+          S[r + 2] = fmaf(1.f - a.z, v, a.z * S[r + 2]);
+          S[r + 3] = fmaf(1.f - a.w, v, a.w * S[r + 3]);
+        } else {
+          S[r] = fmaf(a.x, v, decay * S[r]);
+          S[r + 1] = fmaf(a.y, v, decay * S[r + 1]);
+          S[r + 2] = fmaf(a.z, v, decay * S[r + 2]);
+          S[r + 3] = fmaf(a.w, v, decay * S[r + 3]);
         }
+        o0 = fmaf(S[r], q.x, o0);
+        o1 = fmaf(S[r + 1], q.y, o1);
+        o2 = fmaf(S[r + 2], q.z, o2);
+        o3 = fmaf(S[r + 3], q.w, o3);
       }
-      float o = o0 + o1;
-      for (int w = 1; w < lanes; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-      if (sub == 0 && j < DV) p.out[(int64_t)(t0 + c0 + t) * wide + head * DV + j] = o;
+      float o = (o0 + o1) + (o2 + o3);
+      for (int w = lanes >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+      if (sub == 0 && j < DV) *o_row = o;
     }
+    if (next > 0) stash(smem + (((c0 / CHUNK) + 1) & 1) * per_buffer, next);
     __syncthreads();
   }
 #pragma unroll
@@ -168,14 +227,29 @@ int64_t linear_scan_state_floats(int num_heads, int head_dim, int v_dim) {
   return (int64_t)num_heads * slices * kScanColumns * rows * lanes;
 }
 
-template <typename T, int MODE, int ROWS>
-static int launch_scan(const LinearScanParams& p, int lanes, cudaStream_t stream) {
+template <typename T, int MODE, int ROWS, int CHUNK>
+static int launch_scan_chunk(const LinearScanParams& p, int lanes, cudaStream_t stream) {
   const int slices = (p.v_dim + kScanColumns - 1) / kScanColumns;
   const int64_t blocks = (int64_t)p.num_seqs * p.num_heads * slices;
-  if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
-  const size_t smem = (size_t)kScanChunk * (2 * lanes * ROWS + kScanColumns) * sizeof(float);
-  return (int)launch_chain(linear_scan_kernel<T, MODE, ROWS>, dim3((unsigned)blocks), dim3(kScanColumns * lanes), smem,
-                           stream, dim3(1, 1, 1), p, lanes, slices);
+  if (blocks > 0x7fffffffLL || 2 * p.head_dim + kScanColumns > kScanRounds * kScanColumns * lanes)
+    return (int)cudaErrorInvalidValue;
+  const size_t smem = 2 * (size_t)CHUNK * (2 * lanes * scan_pitch(ROWS, lanes) + kScanColumns) * sizeof(float);
+  auto kernel = linear_scan_kernel<T, MODE, ROWS, CHUNK>;
+  if (smem > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+  }
+  return (int)launch_chain(kernel, dim3((unsigned)blocks), dim3(kScanColumns * lanes), smem, stream, dim3(1, 1, 1), p,
+                           lanes, slices);
+}
+
+// Steps of about a token per sequence (decoding) stage two tokens at a time: fewer registers and less shared memory
+// per block, so more blocks share an SM while the memories stream through; prompts stage sixteen (eight where a lane
+// holds 32 rows).
+template <typename T, int MODE, int ROWS>
+static int launch_scan(const LinearScanParams& p, int lanes, cudaStream_t stream) {
+  if (p.num_tokens <= 2 * (int64_t)p.num_seqs) return launch_scan_chunk<T, MODE, ROWS, 2>(p, lanes, stream);
+  return launch_scan_chunk<T, MODE, ROWS, (ROWS >= 32 ? 8 : 16)>(p, lanes, stream);
 }
 
 template <typename T>

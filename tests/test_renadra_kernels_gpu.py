@@ -135,7 +135,7 @@ class _Case:
                 v_cache[pp, :, :hi - lo] = self.v[s][lo:hi].transpose(0, 1)
         return k_cache.cuda(), v_cache.cuda(), table.cuda()
 
-    def run(self, ops, *, scale, softcap, sigmoid, bias, splits, out_scale=1.0):
+    def run(self, ops, *, scale, softcap, sigmoid, bias, splits, out_scale=1.0, kernel="auto"):
         k_cache, v_cache, table = self.caches()
         q = torch.cat([x.reshape(x.shape[0], -1) for x in self.q]).cuda()
         status = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -143,7 +143,7 @@ class _Case:
             q, k_cache, v_cache, table, _i32(self.cu), _i32(self.ctx_lens), *self.tiles, num_tiles=len(self.tiles[0]),
             q_tile=self.rows, num_splits=splits, num_heads=self.heads, num_kv_heads=self.kv_heads, v_dim=self.vdim,
             scale=scale, window=self.window, softcap=softcap, keep_first=self.keep, sigmoid_weights=sigmoid,
-            head_bias=None if bias is None else bias.cuda(), out_scale=out_scale, status=status)
+            head_bias=None if bias is None else bias.cuda(), out_scale=out_scale, status=status, kernel=kernel)
         assert int(status.item()) == 0
         return out.double().cpu()
 
@@ -188,6 +188,32 @@ def test_attention_with_kept_first_keys_prompts_and_decoded_tokens(dtype, sigmoi
     for splits in (1, 2, 5):
         torch.testing.assert_close(case.run(ops, splits=splits, out_scale=0.8, **kw), case.reference(out_scale=0.8, **kw),
                                    **TOL[dtype])
+
+
+@pytest.mark.parametrize("sigmoid", [True, False])
+@pytest.mark.parametrize("heads,kv_heads,page,window,keep", [(8, 2, 16, 200, 70), (4, 4, 64, 130, 64), (16, 2, 32, 257, 1),
+                                                             (8, 1, 128, 96, 130), (8, 2, 16, 300, 0)])
+def test_prompt_tiles_of_128_dims_on_the_tensor_cores(sigmoid, heads, kv_heads, page, window, keep):
+    """bfloat16 heads of 128 dims take the tcgen05 prompt kernel: kept keys whose count is no multiple of a block or a
+    box, windows that start right behind them, among them and far from them, pages between the two that were given
+    back, portions of two tokens and of one, against the plain attention and against the general kernel."""
+    ops = _ops()
+    dtype, dim = torch.bfloat16, 128
+    assert ops.scored_takes_tensor_cores(dtype, dim, dim, heads // kv_heads, page, prompt=True)
+    q_tile = ops.attention_q_tile(dim, heads // kv_heads)
+    bias = torch.linspace(-3.0, -1.0, heads) if sigmoid else None
+    kw = dict(scale=1.3 * dim ** -0.5, softcap=8.0, sigmoid=sigmoid, bias=bias, out_scale=0.7)
+    q_lens = [150, 40, 2, 1, 333, 64]
+    ctx_lens = [150, 700, keep + window + 9, 1, 333 + window + keep + 61, max(64, keep + 70)]
+    case = _Case(dtype, heads, kv_heads, dim, dim, page, q_lens, ctx_lens, window, keep, seed=21, q_tile=q_tile)
+    got = case.run(ops, splits=1, **kw)
+    want = case.reference(**kw)
+    assert bool(torch.isfinite(got).all())
+    # weights rounded to bfloat16 before they meet the values: a few parts in a thousand of a row's scale
+    scale = want.abs().amax(dim=-1, keepdim=True).clamp_min(1e-3)
+    assert float(((got - want).abs() / scale).max()) < 2.5e-2
+    general = case.run(ops, splits=1, kernel="general", **kw)
+    assert float(((got - general).abs() / scale).max()) < 2.5e-2
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
