@@ -85,6 +85,10 @@ struct TcParams {
   const float* slopes = nullptr;
   int chunk = 0;
   const float* gate = nullptr;
+  int keep_first = 0;
+  int sigmoid = 0;
+  const float* head_bias = nullptr;
+  float out_scale = 1.f;
 };
 
 // Byte offset of (key k, 16-byte chunk c of the head) inside one stage's K or V area.  The area is laid out
@@ -558,14 +562,34 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
   lo = max(lo, first_key);
   lo = lo / tp.box_rows * tp.box_rows;
   const int hi = pos + 1;
-  int range_lo = lo, range_hi = hi;
-  if (p.num_splits > 1) {
-    int per = (hi - lo + p.num_splits - 1) / p.num_splits;
-    per = (per + KT - 1) / KT * KT;
-    range_lo = lo + split * per;
-    range_hi = min(hi, range_lo + per);
+  // Kept first keys: the walk is over a row of blocks, those of the kept keys first (`kept_walk` places, a whole
+  // number of blocks), then the window's from its first box on.  Only boxes that hold a kept key are fetched (the
+  // pages behind them may have been given back); the rows after them count as past the end.  When the window's first
+  // box follows the kept boxes directly, or lies among them, the walk is one run from key 0 and the mask does the
+  // rest.  The splits cut the row of blocks, not the keys.
+  const int keep = kScored ? tp.keep_first : 0;
+  const bool sigmoid = kScored && tp.sigmoid != 0;
+  int kept_hi = 0, kept_walk = 0;
+  if (keep > 0) {
+    kept_hi = (keep + tp.box_rows - 1) / tp.box_rows * tp.box_rows;
+    if (lo > kept_hi) kept_walk = (kept_hi + KT - 1) / KT * KT;
+    else lo = 0;
   }
-  const int num_blocks = range_hi > range_lo ? (range_hi - range_lo + KT - 1) / KT : 0;
+  const int walk = kept_walk + (hi - lo);
+  int walk_lo = 0, walk_hi = walk;
+  if (p.num_splits > 1) {
+    int per = (walk + p.num_splits - 1) / p.num_splits;
+    per = (per + KT - 1) / KT * KT;
+    walk_lo = split * per;
+    walk_hi = min(walk, walk_lo + per);
+  }
+  const int num_blocks = walk_hi > walk_lo ? (walk_hi - walk_lo + KT - 1) / KT : 0;
+  // first key of block b, and the key before which its keys end
+  auto key0_of = [&](int b) -> int {
+    const int at = walk_lo + b * KT;
+    return at < kept_walk ? at : lo + (at - kept_walk);
+  };
+  auto end_of = [&](int b) -> int { return walk_lo + b * KT < kept_walk ? kept_hi : lo + (walk_hi - kept_walk); };
 
   if (tid == 0) {
 #pragma unroll
@@ -578,7 +602,9 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
   __syncthreads();
 
   bool ok = true;
-  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+  // weights that are not normed over the keys have no reference maximum: it stays zero and nothing is rescaled
+  const float m_start = sigmoid ? 0.f : -CUDART_INF_F;
+  float m[2] = {m_start, m_start}, l[2] = {0.f, 0.f};
   float o[NV][4];
 #pragma unroll
   for (int v = 0; v < NV; ++v) o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f;
@@ -589,8 +615,8 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
     // kernel (which writes this step's K and V) still runs, as far as the ring has room.
     const int first_new = ctx - q_len;
     int b = 0;
-    for (; b < num_blocks && b < STAGES && min(range_lo + (b + 1) * KT, range_hi) <= first_new; ++b)
-      issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi, smem + b * Layout::kStage,
+    for (; b < num_blocks && b < STAGES && min(key0_of(b) + KT, end_of(b)) <= first_new; ++b)
+      issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, key0_of(b), end_of(b), smem + b * Layout::kStage,
                          &full[b], 0, 1);
     pdl_wait();      // this step's K/V pages come from the previous kernels
     for (; b < num_blocks; ++b) {
@@ -599,7 +625,7 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
         ok = false;
         break;
       }
-      issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, range_lo + b * KT, range_hi, smem + s * Layout::kStage,
+      issue_block<D, KT>(tp, &k_map, &v_map, window, kvh, key0_of(b), end_of(b), smem + s * Layout::kStage,
                          &full[s], 0, 1);
     }
   } else {
@@ -634,6 +660,11 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
       if (live[1]) slope[1] = tp.slopes[kvh * G + row_b];
     }
     const float inv_cap = (kScored && tp.softcap > 0.f) ? 1.f / tp.softcap : 0.f;
+    float head_bias[2] = {0.f, 0.f};      // inside the sigmoid, in log2 units
+    if (sigmoid && tp.head_bias != nullptr) {
+      if (live[0]) head_bias[0] = tp.head_bias[kvh * G + row_a] * kLog2e;
+      if (live[1]) head_bias[1] = tp.head_bias[kvh * G + row_b] * kLog2e;
+    }
 
     for (int b = 0; b < num_blocks; ++b) {
       const int s = b % STAGES;
@@ -642,8 +673,8 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
       float* my_max = smax + (b & 1) * kCoopWarps * 16;
       __nv_bfloat16* my_p = ptile + (b & 1) * 16 * kPRow;
       if (ok && !mbar_wait(&full[s], (b / STAGES) & 1)) ok = false;
-      const int key0 = range_lo + b * KT;
-      const int nvalid = min(KT, range_hi - key0);
+      const int key0 = key0_of(b);
+      const int nvalid = min(KT, end_of(b) - key0);
       if (nvalid < KT) zero_v_rows<D, KT>(stage, nvalid, tid, kCoopWarps * 32);   // made visible by the barriers below
 
       // scores of this warp's keys: NQ tiles of 8
@@ -672,13 +703,14 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
           const int in_block = (warp * NQ + j) * 8 + (lane & 3) * 2 + (e & 1);
           const int key = key0 + in_block;
           const bool visible = ok && live[r] && in_block < nvalid && key <= pos &&
-                               (p.window <= 0 || key > pos - p.window) && (!kScored || key >= first_key);
+                               (p.window <= 0 || key > pos - p.window || key < keep) &&
+                               (!kScored || key >= first_key);
           if (kScored) {
             // through the cap (tanh x = 1 - 2 / (2^(2 x log2 e) + 1)), less the distance bias, into log2 units
             float x = sc[j][e] * p.scale;
             if (tp.softcap > 0.f) x = tp.softcap * (1.f - __fdividef(2.f, exp2f(x * inv_cap * (2.f * kLog2e)) + 1.f));
             x = fmaf(-slope[r], (float)(pos - key), x);
-            sc[j][e] = visible ? x * kLog2e : -CUDART_INF_F;
+            sc[j][e] = visible ? fmaf(x, kLog2e, head_bias[r]) : -CUDART_INF_F;
           } else {
             sc[j][e] = visible ? sc[j][e] * scale_log2 : -CUDART_INF_F;
           }
@@ -700,9 +732,11 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
       for (int r = 0; r < 2; ++r) {
         const int row = r ? row_b : row_a;
         float mx = m[r];
+        if (!sigmoid) {
 #pragma unroll
-        for (int w = 0; w < kCoopWarps; ++w) mx = fmaxf(mx, my_max[w * 16 + row]);
-        alpha[r] = (mx == -CUDART_INF_F) ? 1.f : exp2f(m[r] - mx);
+          for (int w = 0; w < kCoopWarps; ++w) mx = fmaxf(mx, my_max[w * 16 + row]);
+        }
+        alpha[r] = (mx == -CUDART_INF_F || sigmoid) ? 1.f : exp2f(m[r] - mx);
         m[r] = mx;
         l[r] *= alpha[r];
       }
@@ -712,7 +746,8 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int r = e >> 1;
-          pr[e] = (sc[j][e] == -CUDART_INF_F) ? 0.f : exp2f(sc[j][e] - m[r]);
+          if (sigmoid) pr[e] = (sc[j][e] == -CUDART_INF_F) ? 0.f : __fdividef(1.f, 1.f + exp2f(-sc[j][e]));
+          else pr[e] = (sc[j][e] == -CUDART_INF_F) ? 0.f : exp2f(sc[j][e] - m[r]);
           l[r] += pr[e];
         }
         const int col = (warp * NQ + j) * 8 + (lane & 3) * 2;
@@ -782,7 +817,12 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
           float total = 0.f;
 #pragma unroll
           for (int w = 0; w < kCoopWarps; ++w) total += lpart[w * 16 + row];     // fixed order
-          // a head's gate: every use of the row sum divides by it, so the sum over the gate gates the output
+          // weights that are not normed: every split's maximum is zero, and the sums that the output is divided
+          // by add up to one over the splits
+          if (sigmoid) total = 1.f / (float)p.num_splits;
+          // a head's gate and the output factor: every use of the row sum divides by it, so the sum over the gate
+          // gates the output
+          if (kScored) total = total / tp.out_scale;
           if (kScored && tp.gate != nullptr) total = total / tp.gate[(int64_t)q0 * NH + kvh * G + row];
           merge[row * kRow + D + 1] = total;
         }
@@ -911,7 +951,8 @@ int launch_coop_scored(const ScoredAttentionParams& sp, int box_rows, const CUte
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
-  TcParams tp{p, box_rows, sp.softcap, sp.slopes, sp.chunk, sp.gate};
+  TcParams tp{p, box_rows, sp.softcap, sp.slopes, sp.chunk, sp.gate,
+              sp.keep_first, sp.sigmoid_weights, sp.head_bias, sp.out_scale};
   const dim3 grid((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, (unsigned)p.num_splits);
   const dim3 cluster(1, 1, CLUSTER ? (unsigned)p.num_splits : 1u);
   return (int)launch_chain(kernel, grid, dim3((kCoopWarps + 1) * 32), smem, stream, cluster, k_map, v_map, tp);
@@ -1000,6 +1041,8 @@ int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream) {
 // of their own; 1, 2, 4 or 8 key splits (more than one: merged inside the kernel by the cluster).
 bool attention_tc_scored_supported(const ScoredAttentionParams& sp) {
   const PagedAttentionParams& p = sp.base;
+  if (sp.keep_first > 0 && (p.window <= 0 || sp.chunk > 0)) return false;
+  if (!(sp.out_scale > 0.f)) return false;      // the factor divides the row sum
   return p.q_tile == 1 && sp.v_dim == p.head_dim && sp.k_row_stride == p.head_dim && sp.v_row_stride == p.head_dim &&
          p.k_cache != p.v_cache && (p.num_splits == 1 || attention_tc_merges_in_kernel(p)) && attention_tc_supported(p);
 }
@@ -1015,7 +1058,7 @@ int launch_attention_tc_scored(const ScoredAttentionParams& sp, cudaStream_t str
   const bool merge = p.num_splits > 1;
   // a block of the token's own positions bounds the walk as a window does
   int64_t bound_keys = (int64_t)p.table_width * p.page_size;
-  if (p.window > 0) bound_keys = p.window;
+  if (p.window > 0) bound_keys = p.window + sp.keep_first;
   if (sp.chunk > 0 && sp.chunk < bound_keys) bound_keys = sp.chunk;
   const bool two_warps = decode_config(p.num_splits, bound_keys / p.num_splits / 32) == 6;
 #define AKV_COOP_SCORED(D, W)                                                                   \

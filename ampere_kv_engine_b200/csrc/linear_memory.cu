@@ -10,10 +10,10 @@
 //
 // Work split: a block owns (sequence, head, 32 value columns) for the whole step.  A value column of S lives in the
 // registers of `lanes` neighbouring lanes (ROWS rows each), so writing a token is thread-local and reading it out is
-// one sum over those lanes.  Tokens are staged through two shared-memory buffers CHUNK at a time: a thread loads the
-// next chunk's product columns into registers before it walks the current chunk's tokens, and turns them into
-// activations and gates and stores them afterwards, so that the loads' latency lies behind the walk and there is one
-// block barrier per chunk.  S moves between registers and the request's state slot in an order of its own
+// one sum over those lanes.  Tokens are staged through two shared-memory buffers CHUNK at a time.  In the kernel for
+// prompts a block has further warps that only stage: they load the next chunk's product columns, turn them into
+// activations and gates and store them while the others walk the current chunk's tokens, and there is one block
+// barrier per chunk.  S moves between registers and the request's state slot in an order of its own
 // ([head][slice][row in lane][column][lane]), so that the loads and stores of a decode step are coalesced.
 // Tokens are walked one by one whatever the step holds: the memory after a token does not depend on how the tokens
 // were cut into steps.
@@ -28,18 +28,33 @@ namespace akv {
 namespace {
 
 constexpr int kScanColumns = 32;     // value columns per block
-constexpr int kScanRounds = 3;       // staged entries per thread and token: 2 * dim + 32 <= 3 * threads for every shape
+constexpr int kScanProducers = 128;  // threads that only stage tokens, in the kernel for prompts
+constexpr int kScanBatch = 8;        // tokens whose loads a staging thread has in flight at a time
 
-__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
-__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+// The quotient is a reciprocal and a product (two units in the last place), inline: the staging threads work on many
+// entries at a time and a division's subroutine would put them in a row.  The denominator is at least one; where
+// expf overflows the quotient is zero.
+__device__ __forceinline__ float sigmoid_f(float z) { return __fdividef(1.f, 1.f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return __fdividef(z, 1.f + expf(-z)); }
 
 // floats between two lanes' rows of q (or of a) in shared memory: padded where several lanes share a column, so that
 // the float4 reads of a group's lanes fall into different banks
 __host__ __device__ constexpr int scan_pitch(int rows, int lanes) { return lanes > 1 ? rows + 4 : rows; }
 
-template <typename T, int MODE, int ROWS, int CHUNK>
-__global__ void __launch_bounds__(256)
+// staged entries per staging thread and token: [q (dim) | f or k (dim) | v (32)] over 32 * lanes threads (dim at most
+// rows * lanes), or over the producers (dim at most 8 * rows)
+__host__ __device__ constexpr int scan_rounds(int rows, int producers) {
+  return producers > 0 ? (2 * 8 * rows + kScanColumns + producers - 1) / producers : 3;
+}
+
+// PRODUCERS == 0: every thread owns rows of S and stages its share of a chunk before the walk (steps of a token or
+// two per sequence).  PRODUCERS > 0: that many further threads do nothing but stage, so that loads, activations and
+// gates of the next chunk run beside the walk of the current one.
+template <typename T, int MODE, int ROWS, int CHUNK, int PRODUCERS>
+__global__ void __launch_bounds__(256 + PRODUCERS)
 linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
+  constexpr int kRounds = scan_rounds(ROWS, PRODUCERS);
+  constexpr int kBatch = CHUNK < kScanBatch ? CHUNK : (ROWS >= 32 ? kScanBatch / 2 : kScanBatch);
   pdl_launch_dependents();
   pdl_wait();
   const int H = p.num_heads, D = p.head_dim, DV = p.v_dim;
@@ -50,7 +65,12 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   const int t0 = p.cu_q[seq];
   const int n = p.cu_q[seq + 1] - t0;
   if (slot < 0 || n <= 0) return;                      // a padded sequence: nothing is read or written
-  const int tid = threadIdx.x, threads = blockDim.x;
+  const int tid = threadIdx.x;
+  const int threads = kScanColumns * lanes;            // threads that own rows of S
+  const bool walker = tid < threads;
+  const bool stager = PRODUCERS > 0 ? !walker : true;
+  const int stage_id = PRODUCERS > 0 ? tid - threads : tid;
+  const int stagers = PRODUCERS > 0 ? PRODUCERS : threads;
   const int sub = tid % lanes, col = tid / lanes;
   const int j = slice * kScanColumns + col;
   const int pitch = scan_pitch(ROWS, lanes);
@@ -63,25 +83,28 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   float* mem = p.state + (int64_t)slot * p.state_stride +
                ((int64_t)head * slices + slice) * ROWS * (int64_t)threads + tid;
   float S[ROWS];
+  if (walker) {
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r) S[r] = mem[(int64_t)r * threads];
+    for (int r = 0; r < ROWS; ++r) S[r] = mem[(int64_t)r * threads];
+  }
   const float decay = MODE == kConstantDecay ? p.decay[head] : 0.f;
 
-  // What a thread stages of every token: entry i = tid + round * threads of [q (D) | f or k (D) | v (the slice's
-  // columns)].  Its column of x, its place in a token's shared-memory row and its gate constants are worked out once.
+  // What a staging thread stages of every token: entry i = stage_id + round * stagers of [q (D) | f or k (D) | v (the
+  // slice's columns)].  Its column of x, its place in a token's shared-memory row and its gate constants are worked
+  // out once.
   const int mine_cols = min(kScanColumns, DV - slice * kScanColumns);
   const int fetch_per_token = 2 * D + mine_cols;
-  const T* src[kScanRounds];
-  int dst[kScanRounds], kind[kScanRounds];             // kind 0: q, 1: f or k, 2: v
-  float low[kScanRounds], bias[kScanRounds];
+  const T* src[kRounds];
+  int dst[kRounds], kind[kRounds];                     // kind 0: q, 1: f or k, 2: v
+  float low[kRounds], bias[kRounds];
   const T* x = (const T*)p.x + (int64_t)t0 * p.x_stride;
 #pragma unroll
-  for (int r = 0; r < kScanRounds; ++r) {
-    const int i = tid + r * threads;
+  for (int r = 0; r < kRounds; ++r) {
+    const int i = stage_id + r * stagers;
     src[r] = nullptr;
     dst[r] = kind[r] = 0;
     low[r] = bias[r] = 0.f;
-    if (i < fetch_per_token) {
+    if (stager && i < fetch_per_token) {
       if (i < D) {
         src[r] = x + p.q_off + head * D + i;
         dst[r] = i / ROWS * pitch + i % ROWS;
@@ -101,49 +124,36 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
       }
     }
   }
-  float regs[kScanRounds][CHUNK];
-  auto fetch = [&](int first, int count) {
+  // tokens first .. first + count - 1 of the sequence into a buffer: kBatch tokens' loads at a time, then their
+  // activations and gates
+  auto stage = [&](float* buffer, int first, int count) {
+    for (int tb = 0; tb < count; tb += kBatch) {
+      T raw[kRounds][kBatch];
 #pragma unroll
-    for (int r = 0; r < kScanRounds; ++r) {
+      for (int r = 0; r < kRounds; ++r) {
 #pragma unroll
-      for (int t = 0; t < CHUNK; ++t) {
-        regs[r][t] = 0.f;
-        if (src[r] != nullptr && t < count) regs[r][t] = to_float<T>(src[r][(int64_t)(first + t) * p.x_stride]);
+        for (int t = 0; t < kBatch; ++t)
+          if (src[r] != nullptr && tb + t < count) raw[r][t] = src[r][(int64_t)(first + tb + t) * p.x_stride];
+      }
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) {
+        if (src[r] == nullptr) continue;
+#pragma unroll
+        for (int t = 0; t < kBatch; ++t) {
+          if (tb + t >= count) break;
+          const float z = to_float<T>(raw[r][t]);
+          float y;
+          if (kind[r] == 0) y = silu_f(z);
+          else if (kind[r] == 1) y = MODE == kGatedWrite ? low[r] + (1.f - low[r]) * sigmoid_f(z + bias[r]) : silu_f(z);
+          else y = MODE == kGatedWrite ? z : silu_f(z);
+          buffer[(tb + t) * per_token + dst[r]] = y;
+        }
       }
     }
   };
-  auto stash = [&](float* buffer, int count) {
-#pragma unroll
-    for (int r = 0; r < kScanRounds; ++r) {
-      if (src[r] == nullptr) continue;
-#pragma unroll
-      for (int t = 0; t < CHUNK; ++t) {
-        if (t >= count) break;
-        const float raw = regs[r][t];
-        float y;
-        if (kind[r] == 0) y = silu_f(raw);
-        else if (kind[r] == 1) y = MODE == kGatedWrite ? low[r] + (1.f - low[r]) * sigmoid_f(raw + bias[r]) : silu_f(raw);
-        else y = MODE == kGatedWrite ? raw : silu_f(raw);
-        buffer[t * per_token + dst[r]] = y;
-      }
-    }
-  };
-  // rows of S beyond the dim never change: q and k stay zero there, a forget gate one; value columns beyond the
-  // width stay zero
-  for (int i = tid; i < 2 * per_buffer; i += threads) {
-    const int e = i % per_token;
-    smem[i] = (MODE == kGatedWrite && e >= vec && e < 2 * vec) ? 1.f : 0.f;
-  }
-  __syncthreads();
-  fetch(0, min(CHUNK, n));
-  stash(smem, min(CHUNK, n));
-  __syncthreads();
+  // count tokens of a buffer, one by one; o_row: this thread's column in the first one's output row
   const int wide = H * DV;
-  for (int c0 = 0; c0 < n; c0 += CHUNK) {
-    const int count = min(CHUNK, n - c0), next = min(CHUNK, n - c0 - CHUNK);
-    const float* row = smem + ((c0 / CHUNK) & 1) * per_buffer;
-    if (next > 0) fetch(c0 + CHUNK, next);
-    float* o_row = p.out + (int64_t)(t0 + c0) * wide + head * DV + j;
+  auto walk = [&](const float* row, int count, float* o_row) {
 #pragma unroll 2
     for (int t = 0; t < count; ++t, row += per_token, o_row += wide) {
       const float v = row[2 * vec + col];
@@ -171,14 +181,40 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
         o3 = fmaf(S[r + 3], q.w, o3);
       }
       float o = (o0 + o1) + (o2 + o3);
-      for (int w = lanes >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+#pragma unroll
+      for (int w = 4; w > 0; w >>= 1) {                // at most eight lanes share a column
+        const float other = __shfl_xor_sync(0xffffffffu, o, w);
+        if (w < lanes) o += other;
+      }
       if (sub == 0 && j < DV) *o_row = o;
     }
-    if (next > 0) stash(smem + (((c0 / CHUNK) + 1) & 1) * per_buffer, next);
+  };
+  // rows of S beyond the dim never change: q and k stay zero there, a forget gate one; value columns beyond the
+  // width stay zero
+  for (int i = tid; i < 2 * per_buffer; i += blockDim.x) {
+    const int e = i % per_token;
+    smem[i] = (MODE == kGatedWrite && e >= vec && e < 2 * vec) ? 1.f : 0.f;
+  }
+  __syncthreads();
+  if (stager) stage(smem, 0, min(CHUNK, n));
+  __syncthreads();
+  // every thread of the block meets the one barrier of each chunk, whatever it does in between
+  for (int c0 = 0; c0 < n; c0 += CHUNK) {
+    const int count = min(CHUNK, n - c0), next = min(CHUNK, n - c0 - CHUNK);
+    const int cur = (c0 / CHUNK) & 1;
+    if (PRODUCERS > 0) {
+      if (walker) walk(smem + cur * per_buffer, count, p.out + (int64_t)(t0 + c0) * wide + head * DV + j);
+      else if (next > 0) stage(smem + (cur ^ 1) * per_buffer, c0 + CHUNK, next);
+    } else {
+      walk(smem + cur * per_buffer, count, p.out + (int64_t)(t0 + c0) * wide + head * DV + j);
+      if (next > 0) stage(smem + (cur ^ 1) * per_buffer, c0 + CHUNK, next);
+    }
     __syncthreads();
   }
+  if (walker) {
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r) mem[(int64_t)r * threads] = S[r];
+    for (int r = 0; r < ROWS; ++r) mem[(int64_t)r * threads] = S[r];
+  }
 }
 
 // out[t, c] = in[t, c] / sqrt(mean over c's group of in^2 + eps) * weight[c % weight_len] * factor
@@ -227,29 +263,30 @@ int64_t linear_scan_state_floats(int num_heads, int head_dim, int v_dim) {
   return (int64_t)num_heads * slices * kScanColumns * rows * lanes;
 }
 
-template <typename T, int MODE, int ROWS, int CHUNK>
+template <typename T, int MODE, int ROWS, int CHUNK, int PRODUCERS>
 static int launch_scan_chunk(const LinearScanParams& p, int lanes, cudaStream_t stream) {
   const int slices = (p.v_dim + kScanColumns - 1) / kScanColumns;
   const int64_t blocks = (int64_t)p.num_seqs * p.num_heads * slices;
-  if (blocks > 0x7fffffffLL || 2 * p.head_dim + kScanColumns > kScanRounds * kScanColumns * lanes)
+  const int stagers = PRODUCERS > 0 ? PRODUCERS : kScanColumns * lanes;
+  if (blocks > 0x7fffffffLL || 2 * p.head_dim + kScanColumns > scan_rounds(ROWS, PRODUCERS) * stagers)
     return (int)cudaErrorInvalidValue;
   const size_t smem = 2 * (size_t)CHUNK * (2 * lanes * scan_pitch(ROWS, lanes) + kScanColumns) * sizeof(float);
-  auto kernel = linear_scan_kernel<T, MODE, ROWS, CHUNK>;
+  auto kernel = linear_scan_kernel<T, MODE, ROWS, CHUNK, PRODUCERS>;
   if (smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
   }
-  return (int)launch_chain(kernel, dim3((unsigned)blocks), dim3(kScanColumns * lanes), smem, stream, dim3(1, 1, 1), p,
-                           lanes, slices);
+  return (int)launch_chain(kernel, dim3((unsigned)blocks), dim3(kScanColumns * lanes + PRODUCERS), smem, stream,
+                           dim3(1, 1, 1), p, lanes, slices);
 }
 
-// Steps of about a token per sequence (decoding) stage two tokens at a time: fewer registers and less shared memory
-// per block, so more blocks share an SM while the memories stream through; prompts stage sixteen (eight where a lane
-// holds 32 rows).
+// Steps of about a token per sequence (decoding) stage two tokens at a time, every thread its share: few registers
+// and little shared memory per block, so more blocks share an SM while the memories stream through.  Prompts stage
+// sixteen (eight where a lane holds 32 rows) in threads of their own.
 template <typename T, int MODE, int ROWS>
 static int launch_scan(const LinearScanParams& p, int lanes, cudaStream_t stream) {
-  if (p.num_tokens <= 2 * (int64_t)p.num_seqs) return launch_scan_chunk<T, MODE, ROWS, 2>(p, lanes, stream);
-  return launch_scan_chunk<T, MODE, ROWS, (ROWS >= 32 ? 8 : 16)>(p, lanes, stream);
+  if (p.num_tokens <= 2 * (int64_t)p.num_seqs) return launch_scan_chunk<T, MODE, ROWS, 2, 0>(p, lanes, stream);
+  return launch_scan_chunk<T, MODE, ROWS, (ROWS >= 32 ? 8 : 16), kScanProducers>(p, lanes, stream);
 }
 
 template <typename T>

@@ -358,13 +358,14 @@ int launch_scored_attention(const ScoredAttentionParams& sp, cudaStream_t stream
       sp.k_row_stride < p.head_dim || sp.v_row_stride < sp.v_dim || sp.chunk < 0 || sp.softcap < 0.f ||
       sp.keep_first < 0 || (sp.keep_first > 0 && (p.window <= 0 || sp.chunk > 0)))
     return (int)cudaErrorInvalidValue;
-  // kept first keys, weights without a softmax and an output factor: the tcgen05 prompt kernel and the general kernel
+  // kept first keys, weights without a softmax and an output factor: the tcgen05 prompt kernel, the tensor-core
+  // kernel for single tokens and the general kernel
   if (p.kernel != 1 && p.q_tile > 1 && attention_tcgen05_scored_supported(sp))
     return launch_attention_tcgen05_scored(sp, stream);
+  if (p.kernel != 1 && p.q_tile == 1 && attention_tc_scored_supported(sp)) return launch_attention_tc_scored(sp, stream);
   const bool general_only = sp.keep_first > 0 || sp.sigmoid_weights || sp.head_bias != nullptr || sp.out_scale != 1.f;
   if (general_only)
     return p.dtype == kBFloat16 ? launch_scored_typed<__nv_bfloat16>(sp, stream) : launch_scored_typed<float>(sp, stream);
-  if (p.kernel != 1 && p.q_tile == 1 && attention_tc_scored_supported(sp)) return launch_attention_tc_scored(sp, stream);
   if (p.kernel != 1 && scored_attention_mma_supported(sp)) {
     const int err = launch_scored_attention_mma(sp, stream);
     if (err != 0) return err;

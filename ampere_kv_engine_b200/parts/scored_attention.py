@@ -185,9 +185,10 @@ def run_attention(ctx, group, q, k_cache, v_cache, out, *, num_heads, num_kv_hea
                 ctx.tile_nq[lo:hi], num_tiles=hi - lo, q_tile=q_tile, num_splits=splits, num_heads=num_heads,
                 num_kv_heads=num_kv_heads, window=window, scale=scale, status=ctx.status, out=out)
             continue
-        # kept first keys, sigmoid weights and an output factor: the tensor-core prompt kernel takes them, the
-        # tensor-core kernels for single tokens do not
-        general_only = bool(keep_first or sigmoid_weights or head_bias is not None or out_scale != 1.0) and q_tile == 1
+        # kept first keys, sigmoid weights and an output factor: the tensor-core kernels take them where keys and
+        # values have storage of their own (single tokens: with a positive factor)
+        special = bool(keep_first or sigmoid_weights or head_bias is not None or out_scale != 1.0)
+        general_only = special and (k_cache is v_cache or (q_tile == 1 and not out_scale > 0.0))
         tensor_core = not general_only and k_cache is not v_cache and ops.scored_takes_tensor_cores(
             q.dtype, q.shape[1] // num_heads, v_dim, group_size, k_cache.shape[2], prompt=q_tile > 1)
         if not general_only and k_cache is v_cache and ops.shared_rows_take_tensor_cores(q.dtype, q.shape[1] // num_heads, v_dim):

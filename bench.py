@@ -894,7 +894,8 @@ def sukalorn_shape(args, design: str = "sukalorn") -> int:
                     q, k_pages, v_pages, num_splits=s, num_heads=heads, num_kv_heads=kvh, v_dim=dim, scale=dim ** -0.5,
                     softcap=30.0, window=window, keep_first=keep, sigmoid_weights=True, head_bias=head_bias,
                     out_scale=0.8, **lay), pairs, keys,
-                    ops.choose_splits(lay["num_tiles"], kvh, q_tile * group, min(PROMPT_LEN, reach), False)),
+                    1 if q_tile > 1 and tc else ops.choose_splits(lay["num_tiles"], kvh, q_tile * group,
+                                                                  min(PROMPT_LEN, reach), tc)),
                 "window_attention": (lambda s: ops.paged_attention(
                     q, k_pages, v_pages, num_splits=s, num_heads=heads, num_kv_heads=kvh, window=window,
                     scale=dim ** -0.5, **lay), pairs_plain, keys_plain,

@@ -216,6 +216,38 @@ def test_prompt_tiles_of_128_dims_on_the_tensor_cores(sigmoid, heads, kv_heads, 
     assert float(((got - general).abs() / scale).max()) < 2.5e-2
 
 
+@pytest.mark.parametrize("sigmoid", [True, False])
+@pytest.mark.parametrize("heads,kv_heads,dim,page,window,keep", [(8, 2, 128, 16, 200, 70), (4, 4, 64, 64, 130, 64),
+                                                                 (16, 2, 128, 32, 257, 1), (8, 1, 64, 8, 96, 130),
+                                                                 (8, 2, 128, 16, 300, 0)])
+def test_decoded_tokens_of_64_and_128_dims_on_the_tensor_cores(sigmoid, heads, kv_heads, dim, page, window, keep):
+    """Single tokens of bfloat16 heads take the TMA + mma.sync kernel with 1, 2, 4 or 8 key splits: contexts around the
+    kept keys' and the window's sizes, around blocks of 32 keys and page borders, windows that start right behind the
+    kept keys, among them and far from them (the pages between were given back), against the plain attention and
+    against the general kernel."""
+    ops = _ops()
+    dtype = torch.bfloat16
+    assert ops.scored_takes_tensor_cores(dtype, dim, dim, heads // kv_heads, page, prompt=False)
+    bias = torch.linspace(-3.0, -1.0, heads) if sigmoid else None
+    kw = dict(scale=1.3 * dim ** -0.5, softcap=8.0, sigmoid=sigmoid, bias=bias, out_scale=0.7)
+    edge = (keep + 31) // 32 * 32
+    ctx = [1, 2, 31, 32, 33, keep, keep + 1, keep + 2, window - 1, window, window + 1, window + keep, window + keep + 1,
+           window + edge, window + edge + 1, window + edge + page, window + edge + page + 1, 2 * page, 2 * page + 1, 700,
+           1501]
+    ctx = [c for c in ctx if c >= 1]
+    case = _Case(dtype, heads, kv_heads, dim, dim, page, [1] * len(ctx), ctx, window, keep, seed=23)
+    want = case.reference(**kw)
+    scale = want.abs().amax(dim=-1, keepdim=True).clamp_min(1e-3)
+    general = case.run(ops, splits=1, kernel="general", **kw)
+    assert float(((general - want).abs() / scale).max()) < 2.5e-2
+    for splits in (1, 2, 4, 8):
+        got = case.run(ops, splits=splits, **kw)
+        assert bool(torch.isfinite(got).all())
+        # weights rounded to bfloat16 before they meet the values: a few parts in a thousand of a row's scale
+        assert float(((got - want).abs() / scale).max()) < 2.5e-2, splits
+        assert float(((got - general).abs() / scale).max()) < 2.5e-2, splits
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_one_key_decides_inside_and_outside_the_window_and_the_kept_keys(dtype):
     """All values are zero but one key's, whose score is made large: the output is that value where the key is
