@@ -490,9 +490,9 @@ class RenadraLayer:
 class RenadraConfig:
     """config.json of the ``Renadra`` decoder: ``vocab``, ``width``, ``norm.eps``, ``embedding`` (``scale`` and an
     optional ``bigram`` table: ``buckets``, ``mul_prev``, ``mul_cur``), a list of layers and an optional ``loop``
-    (``start``, ``stop``, ``times``: layers start .. stop - 1 run ``times`` times in a row with the same weights).
+    (``start``, ``stop``, ``times``: the run of layers [start, stop) is walked ``times`` times on one set of weights).
     A layer names its mixer (``attention``: rotated queries and keys in neighbouring pairs, unit-RMS values, a window,
-    softmax; ``hgrn2``: a matrix memory per head whose forget gate also decides what is written; ``parallel``: a
+    softmax; ``hgrn2``: a matrix memory per head that writes to a row with one minus its forget gate; ``parallel``: a
     ``left`` attention without a softmax whose values are its unrotated keys, beside a ``right`` linear attention with
     a constant decay per head) and its dense feed-forward (or null).  Every size and constant is read from here."""
 

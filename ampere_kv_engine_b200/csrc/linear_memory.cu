@@ -3,8 +3,8 @@
 //   S_t = diag(a_t) S_(t-1) + k_t v_t^T,      o_t = S_t^T q_t            S: [dim, v_dim] float32 per (request, head)
 //
 // Two ways to fill a_t and k_t from one product's columns:
-//   kGatedWrite      a = f, k = 1 - f with f = lower + (1 - lower) * sigmoid(x_f + bias)  (a forget gate per row that
-//                    also decides what is written), q = silu(x_q), v = x_v
+//   kGatedWrite      a = f, k = 1 - f with f = lower + (1 - lower) * sigmoid(x_f + bias)  (a row keeps f of itself and
+//                    takes 1 - f of the value), q = silu(x_q), v = x_v
 //   kConstantDecay   a = decay[head] for every row, k = silu(x_k), q = silu(x_q), v = silu(x_v)
 // Everything after the product is float32: gates, activations, the memory and both products with it.
 //
@@ -165,10 +165,11 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
         const float4 q = q4[r4], a = a4[r4];
         const int r = r4 * 4;
         if (MODE == kGatedWrite) {
-          S[r] = fmaf(1.f - a.x, v, a.x * S[r]);
-          S[r + 1] = fmaf(1.f - a.y, v, a.y * S[r + 1]);
-          S[r + 2] = fmaf(1.f - a.z, v, a.z * S[r + 2]);
-          S[r + 3] = fmaf(1.f - a.w, v, a.w * S[r + 3]);
+          // f S + (1 - f) v as v + f (S - v): two operations per entry
+          S[r] = fmaf(a.x, S[r] - v, v);
+          S[r + 1] = fmaf(a.y, S[r + 1] - v, v);
+          S[r + 2] = fmaf(a.z, S[r + 2] - v, v);
+          S[r + 3] = fmaf(a.w, S[r + 3] - v, v);
         } else {
           S[r] = fmaf(a.x, v, decay * S[r]);
           S[r + 1] = fmaf(a.y, v, decay * S[r + 1]);

@@ -6,6 +6,7 @@
     python -m ampere_kv_engine_b200.kernels.microbench norm --tokens 2048
     python -m ampere_kv_engine_b200.kernels.microbench chain --tokens 8 [--trace]
     python -m ampere_kv_engine_b200.kernels.microbench delta-scan --tokens 2048 --batch 1 --heads 16 --kv-heads 4
+    python -m ampere_kv_engine_b200.kernels.microbench linear-scan --tokens 2048 --batch 1 --heads 16 [--mode constant_decay]
     python -m ampere_kv_engine_b200.kernels.microbench experts --tokens 2048 --hidden 2048 --intermediate 768
 
 The counterpart of the reference's kernel micro-benchmark (``python -m ampere_kv.paged_decode --benchmark``,
@@ -281,6 +282,37 @@ def bench_delta_scan(args) -> dict:
             "state_gbs": state_bytes / scan_us / 1e3, "us_per_token_of_a_sequence": scan_us / args.tokens}
 
 
+def bench_linear_scan(args) -> dict:
+    """The linear-memory scan over ``batch`` sequences of ``tokens`` rows each (``heads`` memories of ``head_dim`` x
+    ``head_dim``), in the mode ``--mode`` names, and the norm kernel behind it."""
+    device = torch.device("cuda")
+    H, D = args.heads, args.head_dim
+    V = D
+    n = args.batch * args.tokens
+    g = torch.Generator(device=device).manual_seed(0)
+    x = torch.randn((n, 2 * H * D + 2 * H * V), device=device, generator=g).to(torch.bfloat16)
+    floats = ops.linear_scan_state_floats(H, D, V)
+    copies = copies_for(args.batch * floats * 4) if args.tokens == 1 else 1
+    states = [torch.zeros((args.batch, floats), device=device) for _ in range(copies)]
+    cu = torch.arange(0, n + 1, args.tokens, dtype=torch.int32, device=device)
+    slots = torch.arange(args.batch, dtype=torch.int32, device=device)
+    kw = dict(num_heads=H, head_dim=D, v_dim=V, q_off=0, k_off=H * D, v_off=2 * H * D, mode=args.mode)
+    if args.mode == "gated_write":
+        kw.update(lower=torch.rand((H * D,), device=device, generator=g) * 0.9,
+                  gate_bias=torch.zeros((H * D,), device=device))
+    else:
+        kw.update(decay=torch.linspace(0.6, 0.999, H, device=device))
+    out = ops.linear_scan(x, states[0], cu, slots, **kw)
+    scan_us = timed(lambda i: ops.linear_scan(x, states[i % copies], cu, slots, **kw), args.calls)
+    weight = torch.ones((H * V,), device=device)
+    norm_us = timed(lambda i: ops.group_norm_gate(out, weight, group=H * V, eps=1e-6, out_dtype=torch.bfloat16, x=x,
+                                                  gate_off=2 * H * D + H * V), args.calls)
+    flops = 5.0 * n * H * D * V
+    return {"scan_us": scan_us, "norm_gate_us": norm_us, "scan_tflops": flops / scan_us / 1e6,
+            "state_gbs": 2.0 * 4 * args.batch * floats / scan_us / 1e3,
+            "us_per_token_of_a_sequence": scan_us / args.tokens}
+
+
 def bench_experts(args) -> dict:
     """The routed experts' grouped products for ``tokens`` tokens: ``experts`` experts of ``intermediate`` x
     ``hidden``, a top of ``top``, random routing."""
@@ -313,7 +345,9 @@ def bench_experts(args) -> dict:
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("kernel", choices=("gemm", "decode-attention", "prefill-attention", "norm", "chain",
-                                           "delta-scan", "experts"))
+                                           "delta-scan", "linear-scan", "experts"))
+    parser.add_argument("--mode", choices=tuple(ops.LINEAR_SCAN_MODES), default="gated_write",
+                        help="linear-scan: the gate-complement write or the constant decay per head")
     parser.add_argument("--experts", type=int, default=32)
     parser.add_argument("--top", type=int, default=4)
     parser.add_argument("--tokens", type=int, default=8)
@@ -344,6 +378,8 @@ def main(argv=None) -> int:
         result = bench_chain(args)
     elif args.kernel == "delta-scan":
         result = bench_delta_scan(args)
+    elif args.kernel == "linear-scan":
+        result = bench_linear_scan(args)
     elif args.kernel == "experts":
         result = bench_experts(args)
     elif args.kernel == "prefill-attention":

@@ -2,7 +2,7 @@
 
     S_t = diag(a_t) S_(t-1) + k_t v_t^T,      o_t = S_t^T q_t            S: [head_dim, v_dim] per (request, head)
 
-``hgrn2``: the forget gate of a row also decides what is written to it.
+``hgrn2``: a row is written with one minus its forget gate.
 
     q = silu(W_q x);  v = W_v x;  f = lower + (1 - lower) * sigmoid(W_f x + bias);   a = f,  k = 1 - f
     y = W_o concat_h( o_h / sqrt(mean(o_h^2) + eps) * norm )          one norm weight [v_dim] shared by the heads

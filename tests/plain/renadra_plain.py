@@ -4,12 +4,12 @@ the engine was given.
 
     x_0      = embed[token] * scale + bigram[(prev * mul_prev + token * mul_cur) mod buckets]   (row `buckets` at t = 0)
     a pass   : x <- x + mixer(norm_1(x));  x <- x + ff(norm_2(x))   for the layers of the pass
-    loop     : layers start .. stop - 1 run `times` times (weights shared, memory per pass); x_0 is added to x before
+    loop     : the run of layers [start, stop) is walked `times` times (one set of weights, a memory per walk); x_0 is added to x before
                every pass but the first
     logits   = head(norm(x))
 
 Mixers: ``attention`` (rotated queries and keys in neighbouring pairs, unit-RMS values, a window, softmax),
-``hgrn2`` (a matrix memory per head whose forget gate also decides what is written), ``parallel`` (attention without
+``hgrn2`` (a matrix memory per head that writes to a row with one minus its forget gate), ``parallel`` (attention without
 a softmax, whose values are its unrotated keys, beside a linear attention with a constant decay per head).
 
 ``raw`` is the configuration as config.json holds it; ``w`` maps tensor names to tensors.
