@@ -1215,6 +1215,13 @@ void linear_scan(const Tensor& x, Tensor& state, const Tensor& cu_q, const Tenso
   }
   AKV_CHECK(mode == akv::kGatedWrite ? lower.has_value() : (mode == akv::kConstantDecay && decay.has_value()),
             "linear_scan: mode 0 needs lower, mode 1 needs decay");
+  // a step that holds more than single tokens: activations and gates are worked out once per token by a kernel of
+  // their own, into scratch that the scan's staging warps copy from
+  Tensor act;
+  if (n > 2 * seqs) {
+    act = at::empty({n, 2 * qk + vw}, x.options().dtype(at::kFloat));
+    p.act = act.data_ptr<float>();
+  }
   p.state = state.data_ptr<float>();
   p.state_stride = state.stride(0);
   p.cu_q = cu_q.data_ptr<int>();

@@ -405,6 +405,8 @@ struct LinearScanParams {
   const float* lower;          // [NH * D] (kGatedWrite)
   const float* decay;          // [NH] (kConstantDecay)
   float* state;                // [slots, state_stride]; a slot's first linear_scan_state_floats() floats are S
+  float* act;                  // [N, 2 * NH * D + NH * DV] float32 scratch for steps that hold prompts, or null:
+                               // q, a-or-k and v after their activations and gates, written by a kernel of its own
   int64_t state_stride;
   const int32_t* cu_q;         // [num_seqs + 1]
   const int32_t* state_slots;  // [num_seqs], negative: a padded sequence, left alone

@@ -8,18 +8,26 @@
 //   kConstantDecay   a = decay[head] for every row, k = silu(x_k), q = silu(x_q), v = silu(x_v)
 // Everything after the product is float32: gates, activations, the memory and both products with it.
 //
-// Work split: a block owns (sequence, head, 32 value columns) for the whole step.  A value column of S lives in the
-// registers of `lanes` neighbouring lanes (ROWS rows each), so writing a token is thread-local and reading it out is
-// one sum over those lanes.  Tokens are staged through two shared-memory buffers CHUNK at a time.  In the kernel for
-// prompts a block has further warps that only stage: they load the next chunk's product columns, turn them into
-// activations and gates and store them while the others walk the current chunk's tokens, and there is one block
-// barrier per chunk.  S moves between registers and the request's state slot in an order of its own
-// ([head][slice][row in lane][column][lane]), so that the loads and stores of a decode step are coalesced.
+// Work split: a block owns (sequence, head, 32 value columns) for the whole step; a thread holds ROWS rows of one
+// column of S in registers, `lanes` threads a column, so writing a token is thread-local.  Tokens are staged through
+// two shared-memory buffers CHUNK at a time, and there is one block barrier per chunk.
+//   Decode form (steps of a token or two per sequence): a column's threads are neighbouring lanes and add up their
+//   parts of a token's output with shuffles; every thread stages its share of the next tokens itself (loads,
+//   activations, gates).
+//   Prompt form (everything else): a kernel of its own first writes every token's q, a-or-k and v after activations
+//   and gates as float32 (once per token, not once per block of a head's value slices).  In the scan a warp holds
+//   the same rows of all 32 columns, so its reads of q and of the gates are broadcasts; it leaves its part of every
+//   token's output in shared memory, and when the chunk is walked the walking warps add the parts up, a thread per
+//   (token, column).  Further warps do nothing but copy the next chunk from the float32 scratch, asynchronously.
+// S moves between registers and the request's state slot in an order of its own ([head][slice][row in lane][column]
+// [lane]), the same in both forms, so that the loads and stores of a decode step are coalesced.
 // Tokens are walked one by one whatever the step holds: the memory after a token does not depend on how the tokens
-// were cut into steps.
+// were cut into steps, and a token's output only in the order in which `lanes` parts are added.
 //
 // A second kernel norms what the scan read out: RMS over groups of columns (a head, or all heads together), a
 // weight, a constant factor, and optionally a sigmoid gate from further columns of the product.
+#include <algorithm>
+
 #include "common.cuh"
 #include "launchers.h"
 
@@ -28,8 +36,8 @@ namespace akv {
 namespace {
 
 constexpr int kScanColumns = 32;     // value columns per block
-constexpr int kScanProducers = 128;  // threads that only stage tokens, in the kernel for prompts
-constexpr int kScanBatch = 8;        // tokens whose loads a staging thread has in flight at a time
+constexpr int kScanProducers = 128;  // threads that only copy tokens into shared memory, in the prompt form
+constexpr int kScanBatch = 8;        // tokens whose loads a staging thread has in flight at a time (decode form)
 
 // The quotient is a reciprocal and a product (two units in the last place), inline: the staging threads work on many
 // entries at a time and a division's subroutine would put them in a row.  The denominator is at least one; where
@@ -47,9 +55,51 @@ __host__ __device__ constexpr int scan_rounds(int rows, int producers) {
   return producers > 0 ? (2 * 8 * rows + kScanColumns + producers - 1) / producers : 3;
 }
 
-// PRODUCERS == 0: every thread owns rows of S and stages its share of a chunk before the walk (steps of a token or
-// two per sequence).  PRODUCERS > 0: that many further threads do nothing but stage, so that loads, activations and
-// gates of the next chunk run beside the walk of the current one.
+__device__ __forceinline__ void cp_async_16(void* smem, const void* global) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(global)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void cp_async_4(void* smem, const void* global) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(global)
+               : "memory");
+}
+
+// act[t] = [q (NH * D) | a or k (NH * D) | v (NH * DV)] of token t after activations and gates, float32: what every
+// block of a head's value slices would otherwise work out again for itself while it stages a prompt's tokens.
+template <typename T, int MODE>
+__global__ void linear_prep_kernel(LinearScanParams p, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int qk = p.num_heads * p.head_dim;
+  const int64_t t = blockIdx.x;                        // a block row per token, blockIdx.y over its columns
+  const T* row = (const T*)p.x + t * p.x_stride;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
+    float y;
+    if (c < qk) {
+      y = silu_f(to_float<T>(row[p.q_off + c]));
+    } else if (c < 2 * qk) {
+      const int ch = c - qk;
+      const float z = to_float<T>(row[p.k_off + ch]);
+      if (MODE == kGatedWrite) {
+        const float low = p.lower[ch];
+        y = low + (1.f - low) * sigmoid_f(z + (p.gate_bias != nullptr ? p.gate_bias[ch] : 0.f));
+      } else {
+        y = silu_f(z);
+      }
+    } else {
+      const float z = to_float<T>(row[p.v_off + c - 2 * qk]);
+      y = MODE == kGatedWrite ? z : silu_f(z);
+    }
+    p.act[t * width + c] = y;
+  }
+}
+
+// PRODUCERS == 0: the decode form.  PRODUCERS > 0: the prompt form with that many further threads that only copy
+// the next chunk from p.act into shared memory beside the walk of the current one.
 template <typename T, int MODE, int ROWS, int CHUNK, int PRODUCERS>
 __global__ void __launch_bounds__(256 + PRODUCERS)
 linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
@@ -71,7 +121,11 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   const bool stager = PRODUCERS > 0 ? !walker : true;
   const int stage_id = PRODUCERS > 0 ? tid - threads : tid;
   const int stagers = PRODUCERS > 0 ? PRODUCERS : threads;
-  const int sub = tid % lanes, col = tid / lanes;
+  // which rows (sub) of which column (col) of S a thread owns.  Decode form: a column's lanes are neighbours, so that
+  // they can add up with shuffles.  Prompt form: a warp holds the same rows of all 32 columns, so that its reads of
+  // q and of the gates are one broadcast each and no shuffle stands between two tokens.
+  const int sub = PRODUCERS > 0 ? tid / kScanColumns : tid % lanes;
+  const int col = PRODUCERS > 0 ? tid % kScanColumns : tid / lanes;
   const int j = slice * kScanColumns + col;
   const int pitch = scan_pitch(ROWS, lanes);
   const int vec = lanes * pitch;                       // floats of a token's q (or a) in shared memory
@@ -81,7 +135,7 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   extern __shared__ __align__(16) float smem[];
 
   float* mem = p.state + (int64_t)slot * p.state_stride +
-               ((int64_t)head * slices + slice) * ROWS * (int64_t)threads + tid;
+               ((int64_t)head * slices + slice) * ROWS * (int64_t)threads + col * lanes + sub;
   float S[ROWS];
   if (walker) {
 #pragma unroll
@@ -104,7 +158,7 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
     src[r] = nullptr;
     dst[r] = kind[r] = 0;
     low[r] = bias[r] = 0.f;
-    if (stager && i < fetch_per_token) {
+    if (PRODUCERS == 0 && i < fetch_per_token) {
       if (i < D) {
         src[r] = x + p.q_off + head * D + i;
         dst[r] = i / ROWS * pitch + i % ROWS;
@@ -151,43 +205,103 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
       }
     }
   };
-  // count tokens of a buffer, one by one; o_row: this thread's column in the first one's output row
+  // the same from the scratch that the preparing kernel filled (prompt form): asynchronous copies of 16 bytes where
+  // the widths allow it, of 4 otherwise, all of a chunk in flight at once
+  auto stage_copy = [&](float* buffer, int first, int count) {
+    const int qk = H * D, width = 2 * qk + H * DV;
+    const bool wide_copy = D % 4 == 0 && DV % 4 == 0;
+    const int step = wide_copy ? 4 : 1;
+    const int per = fetch_per_token / step;
+    const float* base = p.act + (int64_t)(t0 + first) * width;
+    for (int e = stage_id; e < count * per; e += stagers) {
+      const int t = e / per, i = (e % per) * step;
+      const float* from = base + (int64_t)t * width;
+      float* to = buffer + t * per_token;
+      if (i < D) {
+        from += head * D + i;
+        to += i / ROWS * pitch + i % ROWS;
+      } else if (i < 2 * D) {
+        from += qk + head * D + (i - D);
+        to += vec + (i - D) / ROWS * pitch + (i - D) % ROWS;
+      } else {
+        from += 2 * qk + head * DV + slice * kScanColumns + (i - 2 * D);
+        to += 2 * vec + (i - 2 * D);
+      }
+      if (wide_copy) cp_async_16(to, from);
+      else cp_async_4(to, from);
+    }
+    cp_async_wait_all();
+  };
+  // a token's q, a and v applied to this thread's rows of S; returns its part of the token's output
+  auto apply_loaded = [&](const float4 (&qs)[ROWS / 4], const float4 (&as)[ROWS / 4], float v) -> float {
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+    for (int r4 = 0; r4 < ROWS / 4; ++r4) {
+      const float4 q = qs[r4], a = as[r4];
+      const int r = r4 * 4;
+      if (MODE == kGatedWrite) {
+        // f S + (1 - f) v as v + f (S - v): two operations per entry
+        S[r] = fmaf(a.x, S[r] - v, v);
+        S[r + 1] = fmaf(a.y, S[r + 1] - v, v);
+        S[r + 2] = fmaf(a.z, S[r + 2] - v, v);
+        S[r + 3] = fmaf(a.w, S[r + 3] - v, v);
+      } else {
+        S[r] = fmaf(a.x, v, decay * S[r]);
+        S[r + 1] = fmaf(a.y, v, decay * S[r + 1]);
+        S[r + 2] = fmaf(a.z, v, decay * S[r + 2]);
+        S[r + 3] = fmaf(a.w, v, decay * S[r + 3]);
+      }
+      o0 = fmaf(S[r], q.x, o0);
+      o1 = fmaf(S[r + 1], q.y, o1);
+      o2 = fmaf(S[r + 2], q.z, o2);
+      o3 = fmaf(S[r + 3], q.w, o3);
+    }
+    return (o0 + o1) + (o2 + o3);
+  };
+  // a token's row of [q | a | v] in shared memory into registers
+  auto fetch = [&](const float* row, float4 (&qs)[ROWS / 4], float4 (&as)[ROWS / 4], float& v) {
+    v = row[2 * vec + col];
+    const float4* q4 = reinterpret_cast<const float4*>(row + sub * pitch);
+    const float4* a4 = reinterpret_cast<const float4*>(row + vec + sub * pitch);
+#pragma unroll
+    for (int r4 = 0; r4 < ROWS / 4; ++r4) {
+      qs[r4] = q4[r4];
+      as[r4] = a4[r4];
+    }
+  };
+  auto apply = [&](const float* row) -> float {
+    float4 qs[ROWS / 4], as[ROWS / 4];
+    float v;
+    fetch(row, qs, as, v);
+    return apply_loaded(qs, as, v);
+  };
   const int wide = H * DV;
+  // count tokens of a buffer in their order, decode form: the lanes that share a column add up their parts of a
+  // token's output in three shuffle steps; o_row: this thread's column in the first token's output row
   auto walk = [&](const float* row, int count, float* o_row) {
 #pragma unroll 2
     for (int t = 0; t < count; ++t, row += per_token, o_row += wide) {
-      const float v = row[2 * vec + col];
-      const float4* q4 = reinterpret_cast<const float4*>(row + sub * pitch);
-      const float4* a4 = reinterpret_cast<const float4*>(row + vec + sub * pitch);
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-#pragma unroll
-      for (int r4 = 0; r4 < ROWS / 4; ++r4) {
-        const float4 q = q4[r4], a = a4[r4];
-        const int r = r4 * 4;
-        if (MODE == kGatedWrite) {
-          // f S + (1 - f) v as v + f (S - v): two operations per entry
-          S[r] = fmaf(a.x, S[r] - v, v);
-          S[r + 1] = fmaf(a.y, S[r + 1] - v, v);
-          S[r + 2] = fmaf(a.z, S[r + 2] - v, v);
-          S[r + 3] = fmaf(a.w, S[r + 3] - v, v);
-        } else {
-          S[r] = fmaf(a.x, v, decay * S[r]);
-          S[r + 1] = fmaf(a.y, v, decay * S[r + 1]);
-          S[r + 2] = fmaf(a.z, v, decay * S[r + 2]);
-          S[r + 3] = fmaf(a.w, v, decay * S[r + 3]);
-        }
-        o0 = fmaf(S[r], q.x, o0);
-        o1 = fmaf(S[r + 1], q.y, o1);
-        o2 = fmaf(S[r + 2], q.z, o2);
-        o3 = fmaf(S[r + 3], q.w, o3);
-      }
-      float o = (o0 + o1) + (o2 + o3);
+      float o = apply(row);
 #pragma unroll
       for (int w = 4; w > 0; w >>= 1) {                // at most eight lanes share a column
         const float other = __shfl_xor_sync(0xffffffffu, o, w);
         if (w < lanes) o += other;
       }
       if (sub == 0 && j < DV) *o_row = o;
+    }
+  };
+  // the same, prompt form: a warp leaves its rows' part of every token's output in shared memory; when the chunk is
+  // walked, the walking warps meet and add the parts up, a thread per (token, column), and store whole rows
+  float* parts = smem + 2 * per_buffer;                // [CHUNK][lanes][32]
+  auto walk_parts = [&](const float* row, int count, float* o_rows) {
+#pragma unroll 2
+    for (int t = 0; t < count; ++t, row += per_token) parts[(t * lanes + sub) * kScanColumns + col] = apply(row);
+    asm volatile("bar.sync 2, %0;" ::"r"(threads) : "memory");
+    for (int i = tid; i < count * kScanColumns; i += threads) {
+      const int t = i / kScanColumns, c = i % kScanColumns;
+      float o = parts[t * lanes * kScanColumns + c];
+      for (int w = 1; w < lanes; ++w) o += parts[(t * lanes + w) * kScanColumns + c];
+      if (slice * kScanColumns + c < DV) o_rows[(int64_t)t * wide + c] = o;
     }
   };
   // rows of S beyond the dim never change: q and k stay zero there, a forget gate one; value columns beyond the
@@ -197,20 +311,38 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
     smem[i] = (MODE == kGatedWrite && e >= vec && e < 2 * vec) ? 1.f : 0.f;
   }
   __syncthreads();
-  if (stager) stage(smem, 0, min(CHUNK, n));
+  if (PRODUCERS > 0) {
+    if (stager) stage_copy(smem, 0, min(CHUNK, n));
+  } else {
+    stage(smem, 0, min(CHUNK, n));
+  }
   __syncthreads();
-  // every thread of the block meets the one barrier of each chunk, whatever it does in between
-  for (int c0 = 0; c0 < n; c0 += CHUNK) {
-    const int count = min(CHUNK, n - c0), next = min(CHUNK, n - c0 - CHUNK);
-    const int cur = (c0 / CHUNK) & 1;
-    if (PRODUCERS > 0) {
-      if (walker) walk(smem + cur * per_buffer, count, p.out + (int64_t)(t0 + c0) * wide + head * DV + j);
-      else if (next > 0) stage(smem + (cur ^ 1) * per_buffer, c0 + CHUNK, next);
+  // Every warp of the block meets one barrier per chunk, whatever it does in between.  With staging warps the two
+  // roles run loops of their own (neither keeps the other's registers alive) and meet at a named barrier that counts
+  // the whole block; a role is whole warps, and both loops have the same number of rounds.
+  if (PRODUCERS > 0) {
+    const unsigned everyone = blockDim.x;
+    if (walker) {
+      for (int c0 = 0; c0 < n; c0 += CHUNK) {
+        walk_parts(smem + ((c0 / CHUNK) & 1) * per_buffer, min(CHUNK, n - c0),
+                   p.out + (int64_t)(t0 + c0) * wide + head * DV + slice * kScanColumns);
+        asm volatile("bar.sync 1, %0;" ::"r"(everyone) : "memory");
+      }
     } else {
+      for (int c0 = 0; c0 < n; c0 += CHUNK) {
+        const int next = min(CHUNK, n - c0 - CHUNK);
+        if (next > 0) stage_copy(smem + (((c0 / CHUNK) & 1) ^ 1) * per_buffer, c0 + CHUNK, next);
+        asm volatile("bar.sync 1, %0;" ::"r"(everyone) : "memory");
+      }
+    }
+  } else {
+    for (int c0 = 0; c0 < n; c0 += CHUNK) {
+      const int count = min(CHUNK, n - c0), next = min(CHUNK, n - c0 - CHUNK);
+      const int cur = (c0 / CHUNK) & 1;
       walk(smem + cur * per_buffer, count, p.out + (int64_t)(t0 + c0) * wide + head * DV + j);
       if (next > 0) stage(smem + (cur ^ 1) * per_buffer, c0 + CHUNK, next);
+      __syncthreads();
     }
-    __syncthreads();
   }
   if (walker) {
 #pragma unroll
@@ -271,7 +403,8 @@ static int launch_scan_chunk(const LinearScanParams& p, int lanes, cudaStream_t 
   const int stagers = PRODUCERS > 0 ? PRODUCERS : kScanColumns * lanes;
   if (blocks > 0x7fffffffLL || 2 * p.head_dim + kScanColumns > scan_rounds(ROWS, PRODUCERS) * stagers)
     return (int)cudaErrorInvalidValue;
-  const size_t smem = 2 * (size_t)CHUNK * (2 * lanes * scan_pitch(ROWS, lanes) + kScanColumns) * sizeof(float);
+  const size_t smem = (2 * (size_t)CHUNK * (2 * lanes * scan_pitch(ROWS, lanes) + kScanColumns) +
+                       (PRODUCERS > 0 ? (size_t)CHUNK * lanes * kScanColumns : 0)) * sizeof(float);
   auto kernel = linear_scan_kernel<T, MODE, ROWS, CHUNK, PRODUCERS>;
   if (smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -281,13 +414,20 @@ static int launch_scan_chunk(const LinearScanParams& p, int lanes, cudaStream_t 
                            dim3(1, 1, 1), p, lanes, slices);
 }
 
-// Steps of about a token per sequence (decoding) stage two tokens at a time, every thread its share: few registers
-// and little shared memory per block, so more blocks share an SM while the memories stream through.  Prompts stage
-// sixteen (eight where a lane holds 32 rows) in threads of their own.
+// Steps of about a token per sequence (decoding; the caller gives no scratch) stage two tokens at a time, every
+// thread its share: few registers and little shared memory per block, so more blocks share an SM while the memories
+// stream through.  Other steps have their activations and gates worked out by a kernel of its own, and the scan
+// stages 32 tokens (eight where a lane holds 32 rows) by asynchronous copies in warps of their own.
 template <typename T, int MODE, int ROWS>
 static int launch_scan(const LinearScanParams& p, int lanes, cudaStream_t stream) {
-  if (p.num_tokens <= 2 * (int64_t)p.num_seqs) return launch_scan_chunk<T, MODE, ROWS, 2, 0>(p, lanes, stream);
-  return launch_scan_chunk<T, MODE, ROWS, (ROWS >= 32 ? 8 : 16), kScanProducers>(p, lanes, stream);
+  if (p.act == nullptr) return launch_scan_chunk<T, MODE, ROWS, 2, 0>(p, lanes, stream);
+  const int width = 2 * p.num_heads * p.head_dim + p.num_heads * p.v_dim;
+  if (p.num_tokens > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  const int across = std::min((width + 255) / 256, 64);
+  const int err = (int)launch_chain(linear_prep_kernel<T, MODE>, dim3((unsigned)p.num_tokens, (unsigned)across),
+                                    dim3(256), 0, stream, dim3(1, 1, 1), p, width);
+  if (err != 0) return err;
+  return launch_scan_chunk<T, MODE, ROWS, (ROWS >= 32 ? 8 : 32), kScanProducers>(p, lanes, stream);
 }
 
 template <typename T>

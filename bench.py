@@ -636,12 +636,19 @@ def sukalorn_shape(args, design: str = "sukalorn") -> int:
         runner.raise_on_status()
         weights = sum(t.numel() * t.element_size() for part in engine.model._parts() for t in vars(part).values()
                       if isinstance(t, torch.Tensor) and t.dim() >= 2)
+        # without the tables a step only gathers rows of (token and pair embeddings): what a decode step reads whole
+        from ampere_kv_engine_b200.parts.embedding import Embedding
+        read = sum(t.numel() * t.element_size() for part in engine.model._parts() if not isinstance(part, Embedding)
+                   for t in vars(part).values() if isinstance(t, torch.Tensor) and t.dim() >= 2)
         del engine, runner, seqs
         torch.cuda.empty_cache()
         return {"prefill_ms": round(prefill_ms, 3), "prefill_tok_s": round(PREFILL_TOKENS / prefill_ms * 1000, 1),
                 "decode_ms": round(decode_ms, 4), "decode_tok_s": round(batch / decode_ms * 1000, 1),
                 "launches_per_decode_step": launches, "matrix_bytes": weights,
-                "decode_hbm_frac_weights_only": round(weights / (decode_ms / 1000) / 1e9 / peaks["hbm_gbs"], 4)}
+                "decode_hbm_frac_weights_only": round(weights / (decode_ms / 1000) / 1e9 / peaks["hbm_gbs"], 4),
+                "matrix_bytes_read": read,
+                "decode_hbm_frac_matrices_read": round(read / (decode_ms / 1000) / 1e9 / peaks["hbm_gbs"], 4),
+                "prefill_matrix_tflops": round(2.0 * (read / 2) * PREFILL_TOKENS / (prefill_ms / 1000) / 1e12, 1)}
 
     def layout(seq_q, q_tile):
         """Batch layout tensors of sequences given as (context, new tokens): (keyword arguments of the attention ops,
