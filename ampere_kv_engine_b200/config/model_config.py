@@ -641,3 +641,170 @@ class RenadraConfig:
         if self.eos_token_id:
             out["eos_token_id"] = list(self.eos_token_id)
         return out
+
+
+@dataclass(frozen=True)
+class ZavizenLayer:
+    """One layer of a Zavizen model as config.json gives it: ``type`` names the mixer, ``mixer`` holds its sizes and
+    constants, ``mlp`` the feed-forward's (None: the layer has none)."""
+
+    type: str
+    mixer: dict
+    mlp: dict | None
+
+    MIXERS = ("parallel", "mamba2")
+
+
+@dataclass(frozen=True)
+class ZavizenConfig:
+    """config.json of the ``Zavizen`` decoder: ``vocab``, ``width``, ``norm.eps``, ``streams`` (copies of the residual
+    stream), a list of layers and an optional ``loop`` (``start``, ``stop``, ``times``: the run of layers [start, stop)
+    is walked ``times`` times on one set of weights).  A layer names its mixer (``parallel``: a ``left`` softmax
+    attention with ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``rot`` beside a ``right`` retention with
+    ``heads``, ``dim``, ``vdim``, ``decay``, ``rot``; ``mamba2``: ``heads``, ``vdim``, ``state``, ``groups``, ``conv``,
+    ``norm_groups``) and its feed-forward (``kind`` ``dense`` with ``ff``, or ``moe`` with ``expert.ff``, ``router``
+    (``experts``, ``top``, ``scale``, optional ``groups`` with ``count`` and ``keep``) and an optional ``shared.ff``;
+    or null).  Every size and constant is read from here."""
+
+    vocab: int
+    width: int
+    norm_eps: float
+    streams: int
+    layers: tuple[ZavizenLayer, ...]
+    loop: dict | None = None
+    max_position_embeddings: int = 1 << 20
+    eos_token_id: tuple[int, ...] = ()
+    architectures: tuple[str, ...] = ("Zavizen",)
+
+    ARCHITECTURE = "Zavizen"
+
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @staticmethod
+    def _check_rot(m: dict, where: str, dim: int) -> None:
+        rot = _section(m, "rot", where)
+        where_r = where + "rot: "
+        dims = _sized(rot, "dims", where_r)
+        if _number(rot, "base", where_r) <= 1:
+            raise ConfigError(f"config.json: {where_r}'base' must be above 1")
+        if dims % 2 or dims > dim:
+            raise ConfigError(f"config.json: {where_r}'dims' must be even and at most 'dim' ({dim}), got {dims}")
+        if rot.get("scaling") is not None:
+            if _number(_section(rot, "scaling", where_r), "factor", where_r + "scaling: ") <= 0:
+                raise ConfigError(f"config.json: {where_r}scaling: 'factor' must be positive")
+
+    @classmethod
+    def _check_mixer(cls, kind: str, m: dict, where: str) -> None:
+        if kind == "mamba2":
+            for key in ("heads", "vdim", "state", "groups", "conv", "norm_groups"):
+                _sized(m, key, where)
+            if m["heads"] % m["groups"]:
+                raise ConfigError(f"config.json: {where}'heads' ({m['heads']}) must be a multiple of 'groups' "
+                                  f"({m['groups']})")
+            if (m["heads"] * m["vdim"]) % m["norm_groups"]:
+                raise ConfigError(f"config.json: {where}'norm_groups' ({m['norm_groups']}) must divide heads * vdim "
+                                  f"({m['heads'] * m['vdim']})")
+            return
+        left, right = _section(m, "left", where), _section(m, "right", where)
+        wl, wr = where + "left: ", where + "right: "
+        for key in ("heads", "kv_heads", "dim", "vdim"):
+            _sized(left, key, wl)
+        if left["heads"] % left["kv_heads"]:
+            raise ConfigError(f"config.json: {wl}'heads' ({left['heads']}) must be a multiple of 'kv_heads' "
+                              f"({left['kv_heads']})")
+        _number(left, "scale", wl)
+        cls._check_rot(left, wl, left["dim"])
+        for key in ("heads", "dim", "vdim"):
+            _sized(right, key, wr)
+        cls._check_rot(right, wr, right["dim"])
+        rates = right.get("decay")
+        if not isinstance(rates, (list, tuple)) or len(rates) != right["heads"] or not all(
+                isinstance(r, (int, float)) and not isinstance(r, bool) and 0 <= r <= 1 for r in rates):
+            raise ConfigError(f"config.json: {wr}'decay' must list a number between 0 and 1 for each of the "
+                              f"{right['heads']} heads")
+
+    @staticmethod
+    def _check_mlp(mlp: dict, where: str) -> None:
+        kind = mlp.get("kind", "dense")
+        if kind == "dense":
+            _sized(mlp, "ff", where)
+            return
+        if kind != "moe":
+            raise ConfigError(f"config.json: {where}'kind' must be 'dense' or 'moe', got {kind!r}")
+        _sized(_section(mlp, "expert", where), "ff", where + "expert: ")
+        router, where_r = _section(mlp, "router", where), where + "router: "
+        experts, top = _sized(router, "experts", where_r), _sized(router, "top", where_r)
+        _number(router, "scale", where_r)
+        count, keep = 1, 1
+        if router.get("groups") is not None:
+            groups = _section(router, "groups", where_r)
+            count, keep = _sized(groups, "count", where_r + "groups: "), _sized(groups, "keep", where_r + "groups: ")
+        if experts % count or keep > count:
+            raise ConfigError(f"config.json: {where_r}{experts} experts do not form {count} equal groups of which "
+                              f"{keep} are kept")
+        if top > keep * (experts // count):
+            raise ConfigError(f"config.json: {where_r}'top' ({top}) is more than the kept groups hold")
+        if mlp.get("shared") is not None:
+            _sized(_section(mlp, "shared", where), "ff", where + "shared: ")
+
+    @classmethod
+    def from_dict(cls, d: dict[str, Any]) -> "ZavizenConfig":
+        layers_raw = d.get("layers")
+        if not isinstance(layers_raw, (list, tuple)) or not layers_raw:
+            raise ConfigError("config.json: key 'layers' must be a non-empty list")
+        layers = []
+        for i, entry in enumerate(layers_raw):
+            where = f"layers[{i}]: "
+            if not isinstance(entry, dict) or entry.get("type") not in ZavizenLayer.MIXERS:
+                raise ConfigError(f"config.json: {where}'type' must be one of {list(ZavizenLayer.MIXERS)}, "
+                                  f"got {entry.get('type') if isinstance(entry, dict) else entry!r}")
+            mixer = _section(entry, "mixer", where)
+            cls._check_mixer(entry["type"], mixer, where + "mixer: ")
+            mlp = entry.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict):
+                    raise ConfigError(f"config.json: {where}'mlp' must be an object or null")
+                cls._check_mlp(mlp, where + "mlp: ")
+            layers.append(ZavizenLayer(entry["type"], copy.deepcopy(mixer), None if mlp is None else copy.deepcopy(mlp)))
+        loop = d.get("loop")
+        if loop is not None:
+            loop = _section(d, "loop", "")
+            times = _sized(loop, "times", "loop: ")
+            start, stop = loop.get("start"), loop.get("stop")
+            if not all(isinstance(v, int) and not isinstance(v, bool) for v in (start, stop)) or \
+                    not 0 <= start < stop <= len(layers):
+                raise ConfigError(f"config.json: loop: 'start' and 'stop' must satisfy 0 <= start < stop <= "
+                                  f"{len(layers)}, got {start!r} and {stop!r}")
+            loop = {"start": start, "stop": stop, "times": times}
+        eos = d.get("eos_token_id")
+        eos = () if eos is None else ((eos,) if isinstance(eos, int) else tuple(eos))
+        cfg = cls(
+            vocab=_sized(d, "vocab", ""),
+            width=_sized(d, "width", ""),
+            norm_eps=_number(_section(d, "norm", ""), "eps", "norm: "),
+            streams=_sized(d, "streams", ""),
+            layers=tuple(layers),
+            loop=loop,
+            max_position_embeddings=_optional(d, "max_position_embeddings", int, 1 << 20),
+            eos_token_id=eos,
+        )
+        if cfg.norm_eps <= 0:
+            raise ConfigError("config.json: norm: 'eps' must be positive")
+        if cfg.streams > 8:
+            raise ConfigError(f"config.json: 'streams' must be at most 8, got {cfg.streams}")
+        return cfg
+
+    def to_dict(self) -> dict[str, Any]:
+        out = {"architecture": self.ARCHITECTURE, "vocab": self.vocab, "width": self.width,
+               "norm": {"eps": self.norm_eps}, "streams": self.streams,
+               "layers": [{"type": l.type, "mixer": copy.deepcopy(l.mixer),
+                           "mlp": None if l.mlp is None else copy.deepcopy(l.mlp)} for l in self.layers]}
+        if self.loop is not None:
+            out["loop"] = dict(self.loop)
+        if self.max_position_embeddings != 1 << 20:
+            out["max_position_embeddings"] = self.max_position_embeddings
+        if self.eos_token_id:
+            out["eos_token_id"] = list(self.eos_token_id)
+        return out

@@ -96,10 +96,17 @@ class ModelSpec:
     #: tensors a checkpoint may carry although nothing uses them (full name -> shape): accepted when present, never
     #: asked for (the second norm of a layer that has no feed-forward, for instance)
     unused_tensors: tuple[tuple[str, tuple[int, ...]], ...] = ()
+    #: copies of the residual stream per token (0: the one plain stream).  With copies the decoder hands the blocks
+    #: [tokens, streams, width], all copies equal to the embedding's row at first, and norms their sum at the end.
+    streams: int = 0
 
     def validate(self) -> None:
         if not self.schedule:
             raise ValueError("model spec: the schedule is empty")
+        if self.streams < 0:
+            raise ValueError("model spec: streams must not be negative")
+        if self.streams and any(e.add_embedding for e in self.schedule):
+            raise ValueError("model spec: adding the embedding again is not defined for a stream in several copies")
         for pos, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"model spec: schedule position {pos} names layer {entry.layer}, "

@@ -1179,13 +1179,20 @@ void delta_scan(const Tensor& qkv, const Tensor& coef, const Tensor& x, const Te
 // [slots, floats per slot] float32 (a view whose rows may be wider than this mixer's share: its stride is passed on).
 void linear_scan(const Tensor& x, Tensor& state, const Tensor& cu_q, const Tensor& state_slots, Tensor& out,
                  int64_t num_heads, int64_t head_dim, int64_t v_dim, int64_t mode, int64_t q_off, int64_t k_off,
-                 int64_t v_off, const OptTensor& gate_bias, const OptTensor& lower, const OptTensor& decay) {
+                 int64_t v_off, const OptTensor& gate_bias, const OptTensor& lower, const OptTensor& decay,
+                 int64_t qk_group, int64_t decay_off) {
   check_cuda(x, "x");
   AKV_CHECK(x.dim() == 2, "x must be [tokens, columns]");
   AKV_CHECK(num_heads > 0 && akv::linear_scan_state_floats((int)num_heads, (int)head_dim, (int)v_dim) > 0,
             "linear_scan: ", num_heads, " heads of ", head_dim, " x ", v_dim, " are outside what the kernel takes (each up to ",
             (int64_t)akv::kLinearScanMaxDim, ")");
-  const int64_t n = x.size(0), qk = num_heads * head_dim, vw = num_heads * v_dim;
+  AKV_CHECK(qk_group >= 1 && num_heads % qk_group == 0, "linear_scan: qk_group must divide the heads");
+  const int64_t n = x.size(0), qk = num_heads / qk_group * head_dim, vw = num_heads * v_dim;
+  const bool prepared = mode == akv::kPlainDecay || mode == akv::kTokenDecay;
+  AKV_CHECK(!prepared || x.scalar_type() == at::kFloat, "linear_scan: modes 2 and 3 read float32 rows");
+  AKV_CHECK(prepared || qk_group == 1, "linear_scan: shared q and k heads come with the prepared modes");
+  AKV_CHECK(mode != akv::kTokenDecay || (decay_off >= 0 && decay_off + num_heads <= x.size(1)),
+            "linear_scan: the decay columns must lie inside x");
   AKV_CHECK(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + qk <= x.size(1) && k_off + qk <= x.size(1) &&
             v_off + vw <= x.size(1), "linear_scan: the q, k and v columns must lie inside x");
   AKV_CHECK(state.is_cuda() && state.scalar_type() == at::kFloat && state.dim() == 2 && state.stride(1) == 1 &&
@@ -1213,15 +1220,23 @@ void linear_scan(const Tensor& x, Tensor& state, const Tensor& cu_q, const Tenso
     check_f32(*decay, "decay", num_heads);
     p.decay = decay->data_ptr<float>();
   }
-  AKV_CHECK(mode == akv::kGatedWrite ? lower.has_value() : (mode == akv::kConstantDecay && decay.has_value()),
-            "linear_scan: mode 0 needs lower, mode 1 needs decay");
+  AKV_CHECK(mode == akv::kGatedWrite ? lower.has_value()
+                                     : (mode == akv::kTokenDecay ||
+                                        ((mode == akv::kConstantDecay || mode == akv::kPlainDecay) && decay.has_value())),
+            "linear_scan: mode 0 needs lower, modes 1 and 2 need decay, mode 3 decay columns");
   // a step that holds more than single tokens: activations and gates are worked out once per token by a kernel of
   // their own, into scratch that the scan's staging warps copy from
   Tensor act;
   if (n > 2 * seqs) {
-    act = at::empty({n, 2 * qk + vw}, x.options().dtype(at::kFloat));
-    p.act = act.data_ptr<float>();
+    if (prepared) {
+      p.act = (float*)x.data_ptr();        // the rows are float32 and final: the staging warps copy from them
+    } else {
+      act = at::empty({n, 2 * qk + vw}, x.options().dtype(at::kFloat));
+      p.act = act.data_ptr<float>();
+    }
   }
+  p.qk_group = (int)qk_group;
+  p.decay_off = (int)decay_off;
   p.state = state.data_ptr<float>();
   p.state_stride = state.stride(0);
   p.cu_q = cu_q.data_ptr<int>();
@@ -1238,38 +1253,65 @@ void linear_scan(const Tensor& x, Tensor& state, const Tensor& cu_q, const Tenso
   check_launch(akv::launch_linear_scan(p, stream_of(x)), "linear_scan");
 }
 
-void group_norm_gate(const Tensor& in, Tensor& out, const Tensor& weight, int64_t group, double eps, double factor,
-                     const OptTensor& x, int64_t gate_off) {
+void group_norm_gate(const Tensor& in, Tensor& out, const OptTensor& weight, int64_t group, double eps, double factor,
+                     const OptTensor& x, int64_t gate_off, int64_t gate_kind, bool gate_first, const OptTensor& skip,
+                     int64_t skip_off, const OptTensor& skip_coef, int64_t skip_head) {
   check_cuda(in, "in");
   check_cuda(out, "out");
   AKV_CHECK(in.scalar_type() == at::kFloat && in.dim() == 2, "in must be float32 [tokens, width]");
   const int64_t n = in.size(0), width = in.size(1);
   AKV_CHECK(out.numel() == n * width, "out must be [tokens, width]");
   AKV_CHECK(group >= 1 && width % group == 0, "group_norm_gate: the group (", group, ") must divide the width (", width, ")");
-  check_cuda(weight, "weight");
-  AKV_CHECK(weight.scalar_type() == at::kFloat && (weight.numel() == group || weight.numel() == width),
-            "weight must be float32 with a group's or the whole width's entries");
-  const void* x_ptr = nullptr;
-  int64_t x_stride = 0;
+  akv::GroupNormGateParams p{};
+  if (weight.has_value()) {
+    check_cuda(*weight, "weight");
+    AKV_CHECK(weight->scalar_type() == at::kFloat && (weight->numel() == group || weight->numel() == width),
+              "weight must be float32 with a group's or the whole width's entries");
+    p.weight = weight->data_ptr<float>();
+    p.weight_len = (int)weight->numel();
+  }
   if (x.has_value()) {
     check_cuda(*x, "x");
     check_same(*x, out, "x", "out");
     AKV_CHECK(x->dim() == 2 && x->size(0) == n && gate_off >= 0 && gate_off + width <= x->size(1),
               "the gate columns must lie inside x");
-    x_ptr = x->data_ptr();
-    x_stride = x->size(1);
+    AKV_CHECK(gate_kind == 0 || gate_kind == 1, "gate_kind: 0 sigmoid, 1 SiLU");
+    p.x = x->data_ptr();
+    p.x_stride = x->size(1);
   }
+  if (skip.has_value()) {
+    check_cuda(*skip, "skip");
+    AKV_CHECK(skip->scalar_type() == at::kFloat && skip->dim() == 2 && skip->size(0) == n && skip_off >= 0 &&
+                  skip_off + width <= skip->size(1), "the skip columns must lie inside skip (float32 [tokens, columns])");
+    AKV_CHECK(skip_coef.has_value() && skip_head >= 1 && width % skip_head == 0,
+              "skip needs a coefficient per run of skip_head columns");
+    check_f32(*skip_coef, "skip_coef", width / skip_head);
+    p.skip = skip->data_ptr<float>();
+    p.skip_stride = skip->size(1);
+    p.skip_off = (int)skip_off;
+    p.skip_coef = skip_coef->data_ptr<float>();
+    p.skip_head = (int)skip_head;
+  }
+  p.in = in.data_ptr<float>();
+  p.out = out.data_ptr();
+  p.num_tokens = n;
+  p.width = (int)width;
+  p.group = (int)group;
+  p.eps = (float)eps;
+  p.factor = (float)factor;
+  p.gate_off = (int)gate_off;
+  p.gate_kind = (int)gate_kind;
+  p.gate_first = gate_first ? 1 : 0;
+  p.dtype = dtype_code(out, "out");
   c10::cuda::CUDAGuard guard(in.device());
-  check_launch(akv::launch_group_norm_gate(in.data_ptr<float>(), out.data_ptr(), weight.data_ptr<float>(),
-                                           (int)weight.numel(), n, (int)width, (int)group, (float)eps, (float)factor,
-                                           x_ptr, x_stride, (int)gate_off, dtype_code(out, "out"), stream_of(in)),
-               "group_norm_gate");
+  check_launch(akv::launch_group_norm_gate(p, stream_of(in)), "group_norm_gate");
 }
 
 void rotary_prep(const Tensor& x, const Tensor& positions, const OptTensor& slots, const Tensor& freq, Tensor& q_out,
                  const OptTensor& k_cache, const OptTensor& v_cache, int64_t num_heads, int64_t num_kv_heads,
                  int64_t head_dim, int64_t v_dim, int64_t rotary_dims, int64_t layout, double factor,
-                 bool value_from_key, bool value_norm, double eps, const OptTensor& status) {
+                 bool value_from_key, bool value_norm, double eps, const OptTensor& status, const OptTensor& q_norm,
+                 const OptTensor& k_norm, double row_norm_eps) {
   check_cuda(x, "x");
   check_cuda(q_out, "q_out");
   check_same(x, q_out, "x", "q_out");
@@ -1317,6 +1359,14 @@ void rotary_prep(const Tensor& x, const Tensor& positions, const OptTensor& slot
   p.value_from_key = value_from_key ? 1 : 0;
   p.value_norm = value_norm ? 1 : 0;
   p.eps = (float)eps;
+  AKV_CHECK(q_norm.has_value() == k_norm.has_value(), "rotary_prep: q_norm and k_norm come together");
+  if (q_norm.has_value()) {
+    check_f32(*q_norm, "q_norm", num_heads * head_dim);
+    check_f32(*k_norm, "k_norm", num_kv_heads * head_dim);
+    p.q_norm = q_norm->data_ptr<float>();
+    p.k_norm = k_norm->data_ptr<float>();
+    p.row_norm_eps = (float)row_norm_eps;
+  }
   p.dtype = dtype_code(x, "x");
   p.status = status_ptr(status);
   c10::cuda::CUDAGuard guard(x.device());
@@ -1384,8 +1434,226 @@ void scaled_sum(const Tensor& a, const Tensor& b, Tensor& out, double sa, double
                                       dtype_code(a, "a"), stream_of(a)), "scaled_sum");
 }
 
+// The q, k and v heads of one product as float32 rows [q | k | v], q and k turned by position (see launchers.h).
+void rotary_rows(const Tensor& x, const Tensor& positions, const Tensor& freq, Tensor& out, int64_t num_heads,
+                 int64_t head_dim, int64_t v_dim, int64_t rotary_dims, int64_t q_off, int64_t k_off, int64_t v_off,
+                 double q_scale, double k_scale) {
+  check_cuda(x, "x");
+  AKV_CHECK(x.dim() == 2 && num_heads > 0 && head_dim > 0 && v_dim > 0, "rotary_rows: x [tokens, columns], positive sizes");
+  AKV_CHECK(rotary_dims >= 0 && rotary_dims % 2 == 0 && rotary_dims <= head_dim,
+            "rotary_rows: rotary_dims must be even and at most the head's width");
+  const int64_t n = x.size(0), qk = num_heads * head_dim, vw = num_heads * v_dim;
+  AKV_CHECK(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + qk <= x.size(1) && k_off + qk <= x.size(1) &&
+            v_off + vw <= x.size(1), "rotary_rows: the q, k and v columns must lie inside x");
+  check_i32(positions, "positions", n);
+  check_f32(freq, "freq", rotary_dims / 2);
+  check_cuda(out, "out");
+  AKV_CHECK(out.scalar_type() == at::kFloat && out.dim() == 2 && out.size(0) == n && out.size(1) >= 2 * qk + vw,
+            "out must be float32 [tokens, at least 2 * heads * head_dim + heads * v_dim]");
+  akv::RotaryRowsParams p{};
+  p.x = x.data_ptr();
+  p.x_stride = x.size(1);
+  p.q_off = (int)q_off;
+  p.k_off = (int)k_off;
+  p.v_off = (int)v_off;
+  p.positions = positions.data_ptr<int>();
+  p.freq = freq.data_ptr<float>();
+  p.out = out.data_ptr<float>();
+  p.out_stride = out.size(1);
+  p.num_tokens = n;
+  p.num_heads = (int)num_heads;
+  p.head_dim = (int)head_dim;
+  p.v_dim = (int)v_dim;
+  p.rotary_dims = (int)rotary_dims;
+  p.q_scale = (float)q_scale;
+  p.k_scale = (float)k_scale;
+  p.dtype = dtype_code(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_rotary_rows(p, stream_of(x)), "rotary_rows");
+}
+
+// Hyper-connections (see launchers.h).  x [tokens, streams, width] float32; y the pending sublayer result.
+akv::HyperStepParams hyper_params(Tensor& x, const OptTensor& y, const OptTensor& mix, const OptTensor& write,
+                                  const OptTensor& scale) {
+  check_cuda(x, "x");
+  AKV_CHECK(x.scalar_type() == at::kFloat && x.dim() == 3, "x must be float32 [tokens, streams, width]");
+  const int64_t n = x.size(0), streams = x.size(1), width = x.size(2);
+  AKV_CHECK(streams >= 1 && streams <= akv::kHyperMaxStreams, "hyper: 1 to ", (int64_t)akv::kHyperMaxStreams, " streams");
+  akv::HyperStepParams p{};
+  p.x = x.data_ptr<float>();
+  p.num_tokens = n;
+  p.streams = (int)streams;
+  p.width = (int)width;
+  if (y.has_value()) {
+    check_cuda(*y, "y");
+    AKV_CHECK(y->numel() == n * width && y->device() == x.device(), "y must be [tokens, width]");
+    AKV_CHECK(mix.has_value() && write.has_value(), "y needs mix and write");
+    check_f32(*mix, "mix", streams * streams);
+    check_f32(*write, "write", streams);
+    p.y = y->data_ptr();
+    p.y_dtype = dtype_code(*y, "y");
+    p.mix = mix->data_ptr<float>();
+    p.write = write->data_ptr<float>();
+    if (scale.has_value()) {
+      check_f32(*scale, "scale", width);
+      p.scale = scale->data_ptr<float>();
+    }
+  }
+  return p;
+}
+
+void hyper_step(Tensor& x, const OptTensor& y, const OptTensor& mix, const OptTensor& write, const OptTensor& scale,
+                const OptTensor& read, const OptTensor& weight, double eps, const OptTensor& out, const OptTensor& rows,
+                const OptTensor& status) {
+  akv::HyperStepParams p = hyper_params(x, y, mix, write, scale);
+  AKV_CHECK(y.has_value() || out.has_value(), "hyper_step: nothing to do");
+  if (out.has_value()) {
+    AKV_CHECK(read.has_value() && weight.has_value(), "out needs read and weight");
+    check_f32(*read, "read", p.streams);
+    check_f32(*weight, "weight", p.width);
+    check_cuda(*out, "out");
+    int64_t out_rows = p.num_tokens;
+    if (rows.has_value()) {
+      AKV_CHECK(!y.has_value(), "hyper_step: gathered rows go without a write");
+      check_i32(*rows, "rows");
+      out_rows = rows->numel();
+      p.rows = rows->data_ptr<int>();
+      p.num_rows = out_rows;
+    }
+    AKV_CHECK(out->numel() == out_rows * p.width && out->device() == x.device(), "out must be [rows, width]");
+    p.read = read->data_ptr<float>();
+    p.weight = weight->data_ptr<float>();
+    p.eps = (float)eps;
+    p.out = out->data_ptr();
+    p.dtype = dtype_code(*out, "out");
+  }
+  p.status = status_ptr(status);
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_hyper_step(p, stream_of(x)), "hyper_step");
+}
+
+void hyper_collapse(Tensor& x, const OptTensor& y, const OptTensor& mix, const OptTensor& write, const OptTensor& scale,
+                    Tensor& sum) {
+  akv::HyperStepParams p = hyper_params(x, y, mix, write, scale);
+  check_f32(sum, "sum", p.num_tokens * p.width);
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_hyper_collapse(p, sum.data_ptr<float>(), stream_of(x)), "hyper_collapse");
+}
+
+void hyper_expand(const Tensor& in, Tensor& x) {
+  check_cuda(x, "x");
+  AKV_CHECK(x.scalar_type() == at::kFloat && x.dim() == 3, "x must be float32 [tokens, streams, width]");
+  check_f32(in, "in", x.size(0) * x.size(2));
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_hyper_expand(in.data_ptr<float>(), x.data_ptr<float>(), x.size(0), (int)x.size(1),
+                                        (int)x.size(2), stream_of(x)), "hyper_expand");
+}
+
+void normed_pair_sum(const Tensor& a, const Tensor& b, const Tensor& wa, const Tensor& wb, Tensor& out, double eps,
+                     double sa, double sb) {
+  check_cuda(out, "out");
+  AKV_CHECK(a.dim() == 2, "a must be [tokens, width]");
+  const int64_t n = a.size(0), width = a.size(1);
+  check_f32(a, "a", n * width);
+  check_f32(b, "b", n * width);
+  check_f32(wa, "wa", width);
+  check_f32(wb, "wb", width);
+  AKV_CHECK(out.numel() == n * width && out.device() == a.device(), "out must be [tokens, width]");
+  c10::cuda::CUDAGuard guard(a.device());
+  check_launch(akv::launch_normed_pair_sum(a.data_ptr<float>(), b.data_ptr<float>(), wa.data_ptr<float>(),
+                                           wb.data_ptr<float>(), out.data_ptr(), n, (int)width, (float)eps, (float)sa,
+                                           (float)sb, dtype_code(out, "out"), stream_of(a)), "normed_pair_sum");
+}
+
+// A selective state-space mixer's preparation (see launchers.h).
+void ssm_prep(const Tensor& x, const Tensor& conv, const OptTensor& conv_bias, const Tensor& step_bias,
+              const Tensor& rate_log, const Tensor& state, int64_t tail_off, const Tensor& cu_q, const Tensor& state_slots,
+              Tensor& out, int64_t num_heads, int64_t v_dim, int64_t state_dim, int64_t groups, int64_t taps,
+              int64_t conv_off, int64_t step_off) {
+  check_cuda(x, "x");
+  AKV_CHECK(x.dim() == 2 && num_heads >= 1 && num_heads <= akv::kSsmMaxHeads && v_dim >= 1 && state_dim >= 1 &&
+                groups >= 1 && num_heads % groups == 0 && taps >= 1 && taps <= akv::kConvMaxTaps,
+            "ssm_prep: up to ", (int64_t)akv::kSsmMaxHeads, " heads in equal groups, 1 to ", (int64_t)akv::kConvMaxTaps, " taps");
+  const int64_t n = x.size(0), inner = num_heads * v_dim, gn = groups * state_dim, channels = inner + 2 * gn;
+  AKV_CHECK(conv_off >= 0 && conv_off + channels <= x.size(1) && step_off >= 0 && step_off + num_heads <= x.size(1),
+            "ssm_prep: the convolved channels and the step columns must lie inside x");
+  check_f32(conv, "conv", channels * taps);
+  check_f32(step_bias, "step_bias", num_heads);
+  check_f32(rate_log, "rate_log", num_heads);
+  AKV_CHECK(state.is_cuda() && state.scalar_type() == at::kFloat && state.dim() == 2 && state.stride(1) == 1 &&
+                tail_off >= 0 && tail_off + (taps - 1) * channels <= state.size(1),
+            "state must be float32 [slots, floats] with room for the convolutions' inputs behind tail_off");
+  check_i32(cu_q, "cu_q");
+  const int64_t seqs = cu_q.numel() - 1;
+  check_i32(state_slots, "state_slots", seqs);
+  check_cuda(out, "out");
+  AKV_CHECK(out.scalar_type() == at::kFloat && out.dim() == 2 && out.size(0) == n && out.size(1) >= 2 * gn + 2 * inner + num_heads,
+            "out must be float32 [tokens, at least 2 * groups * state + 2 * heads * v_dim + heads]");
+  akv::SsmPrepParams p{};
+  p.x = x.data_ptr();
+  p.x_stride = x.size(1);
+  p.conv_off = (int)conv_off;
+  p.step_off = (int)step_off;
+  p.conv = conv.data_ptr<float>();
+  if (conv_bias.has_value()) {
+    check_f32(*conv_bias, "conv_bias", channels);
+    p.conv_bias = conv_bias->data_ptr<float>();
+  }
+  p.step_bias = step_bias.data_ptr<float>();
+  p.rate_log = rate_log.data_ptr<float>();
+  p.state = state.data_ptr<float>();
+  p.state_stride = state.stride(0);
+  p.tail_off = tail_off;
+  p.cu_q = cu_q.data_ptr<int>();
+  p.state_slots = state_slots.data_ptr<int>();
+  p.out = out.data_ptr<float>();
+  p.out_stride = out.size(1);
+  p.num_tokens = n;
+  p.num_seqs = (int)seqs;
+  p.num_slots = (int)state.size(0);
+  p.num_heads = (int)num_heads;
+  p.v_dim = (int)v_dim;
+  p.state_dim = (int)state_dim;
+  p.groups = (int)groups;
+  p.taps = (int)taps;
+  p.dtype = dtype_code(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_ssm_prep(p, stream_of(x)), "ssm_prep");
+}
+
+// The last taps - 1 inputs of `channels` convolved columns of x, per sequence, into the state slot behind tail_off.
+void conv_tail(const Tensor& x, Tensor& state, int64_t tail_off, const Tensor& cu_q, const Tensor& state_slots,
+               int64_t conv_off, int64_t channels, int64_t taps) {
+  check_cuda(x, "x");
+  AKV_CHECK(x.dim() == 2 && channels >= 1 && taps >= 1 && taps <= akv::kConvMaxTaps && conv_off >= 0 &&
+                conv_off + channels <= x.size(1), "conv_tail: the channels must lie inside x; 1 to ",
+            (int64_t)akv::kConvMaxTaps, " taps");
+  AKV_CHECK(state.is_cuda() && state.scalar_type() == at::kFloat && state.dim() == 2 && state.stride(1) == 1 &&
+                tail_off >= 0 && tail_off + (taps - 1) * channels <= state.size(1),
+            "state must be float32 [slots, floats] with room for the inputs behind tail_off");
+  check_i32(cu_q, "cu_q");
+  const int64_t seqs = cu_q.numel() - 1;
+  check_i32(state_slots, "state_slots", seqs);
+  akv::ConvTailParams p{};
+  p.x = x.data_ptr();
+  p.x_stride = x.size(1);
+  p.conv_off = (int)conv_off;
+  p.channels = (int)channels;
+  p.taps = (int)taps;
+  p.state = state.data_ptr<float>();
+  p.state_stride = state.stride(0);
+  p.tail_off = tail_off;
+  p.cu_q = cu_q.data_ptr<int>();
+  p.state_slots = state_slots.data_ptr<int>();
+  p.num_seqs = (int)seqs;
+  p.num_slots = (int)state.size(0);
+  p.dtype = dtype_code(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_conv_tail(p, stream_of(x)), "conv_tail");
+}
+
 void moe_route(const Tensor& logits, const OptTensor& correction, Tensor& chosen, Tensor& weights, int64_t groups,
-               int64_t keep_groups, int64_t group_top, double scale, double weight_eps) {
+               int64_t keep_groups, int64_t group_top, double scale, double weight_eps, int64_t score_kind) {
   check_cuda(logits, "logits");
   AKV_CHECK(logits.scalar_type() == at::kFloat && logits.dim() == 2, "logits must be float32 [tokens, experts]");
   const int64_t n = logits.size(0), experts = logits.size(1);
@@ -1414,6 +1682,8 @@ void moe_route(const Tensor& logits, const OptTensor& correction, Tensor& chosen
   p.group_top = (int)group_top;
   p.scale = (float)scale;
   p.weight_eps = (float)weight_eps;
+  AKV_CHECK(score_kind == 0 || score_kind == 1, "moe_route: score_kind 0 (sigmoid) or 1 (softmax)");
+  p.score_kind = (int)score_kind;
   c10::cuda::CUDAGuard guard(logits.device());
   check_launch(akv::launch_moe_route(p, stream_of(logits)), "moe_route");
 }
@@ -1444,7 +1714,7 @@ void moe_sort(const Tensor& chosen, Tensor& order, Tensor& offsets) {
 }
 
 void moe_gate_up(const Tensor& x, const Tensor& w, const Tensor& order, const Tensor& offsets, Tensor& act, int64_t top,
-                 double limit, double slope, int64_t form) {
+                 double limit, double slope, int64_t form, double up_offset) {
   check_cuda(x, "x");
   check_cuda(w, "w");
   check_cuda(act, "act");
@@ -1470,6 +1740,7 @@ void moe_gate_up(const Tensor& x, const Tensor& w, const Tensor& order, const Te
   p.top = (int)top;
   p.limit = (float)limit;
   p.slope = (float)slope;
+  p.up_offset = (float)up_offset;
   p.dtype = dtype_code(x, "x");
   AKV_CHECK(form >= 0 && form <= 3, "form: 0 by size, 1 float arithmetic, 2 mma.sync tiles, 3 few rows");
   p.force_plain = (int)form;
@@ -1636,28 +1907,49 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("linear_scan", &linear_scan, py::arg("x"), py::arg("state"), py::arg("cu_q"), py::arg("state_slots"),
         py::arg("out"), py::arg("num_heads"), py::arg("head_dim"), py::arg("v_dim"), py::arg("mode"), py::arg("q_off"),
         py::arg("k_off"), py::arg("v_off"), py::arg("gate_bias") = py::none(), py::arg("lower") = py::none(),
-        py::arg("decay") = py::none());
+        py::arg("decay") = py::none(), py::arg("qk_group") = 1, py::arg("decay_off") = 0);
   m.def("linear_scan_state_floats", [](int64_t heads, int64_t dim, int64_t v_dim) {
     return (int64_t)akv::linear_scan_state_floats((int)heads, (int)dim, (int)v_dim);
   });
   m.def("group_norm_gate", &group_norm_gate, py::arg("in"), py::arg("out"), py::arg("weight"), py::arg("group"),
-        py::arg("eps"), py::arg("factor") = 1.0, py::arg("x") = py::none(), py::arg("gate_off") = 0);
+        py::arg("eps"), py::arg("factor") = 1.0, py::arg("x") = py::none(), py::arg("gate_off") = 0,
+        py::arg("gate_kind") = 0, py::arg("gate_first") = false, py::arg("skip") = py::none(), py::arg("skip_off") = 0,
+        py::arg("skip_coef") = py::none(), py::arg("skip_head") = 1);
   m.def("rotary_prep", &rotary_prep, py::arg("x"), py::arg("positions"), py::arg("slots"), py::arg("freq"),
         py::arg("q_out"), py::arg("k_cache"), py::arg("v_cache"), py::arg("num_heads"), py::arg("num_kv_heads"),
         py::arg("head_dim"), py::arg("v_dim"), py::arg("rotary_dims"), py::arg("layout"), py::arg("factor") = 1.0,
         py::arg("value_from_key") = false, py::arg("value_norm") = false, py::arg("eps") = 0.0,
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), py::arg("q_norm") = py::none(), py::arg("k_norm") = py::none(),
+        py::arg("row_norm_eps") = 0.0);
   m.def("pair_rows_add", &pair_rows_add, py::arg("hidden"), py::arg("ids"), py::arg("sampled"), py::arg("positions"),
         py::arg("cu_q"), py::arg("state_slots"), py::arg("last_token"), py::arg("table"), py::arg("vocab"),
         py::arg("buckets"), py::arg("mul_prev"), py::arg("mul_cur"));
   m.def("stream_add", &stream_add, py::arg("hidden"), py::arg("other"));
+  m.def("rotary_rows", &rotary_rows, py::arg("x"), py::arg("positions"), py::arg("freq"), py::arg("out"),
+        py::arg("num_heads"), py::arg("head_dim"), py::arg("v_dim"), py::arg("rotary_dims"), py::arg("q_off"),
+        py::arg("k_off"), py::arg("v_off"), py::arg("q_scale") = 1.0, py::arg("k_scale") = 1.0);
+  m.def("hyper_step", &hyper_step, py::arg("x"), py::arg("y"), py::arg("mix"), py::arg("write"), py::arg("scale"),
+        py::arg("read"), py::arg("weight"), py::arg("eps"), py::arg("out"), py::arg("rows") = py::none(),
+        py::arg("status") = py::none());
+  m.def("hyper_collapse", &hyper_collapse, py::arg("x"), py::arg("y"), py::arg("mix"), py::arg("write"),
+        py::arg("scale"), py::arg("sum"));
+  m.def("hyper_expand", &hyper_expand, py::arg("in"), py::arg("x"));
+  m.def("normed_pair_sum", &normed_pair_sum, py::arg("a"), py::arg("b"), py::arg("wa"), py::arg("wb"), py::arg("out"),
+        py::arg("eps"), py::arg("sa"), py::arg("sb"));
+  m.def("ssm_prep", &ssm_prep, py::arg("x"), py::arg("conv"), py::arg("conv_bias"), py::arg("step_bias"),
+        py::arg("rate_log"), py::arg("state"), py::arg("tail_off"), py::arg("cu_q"), py::arg("state_slots"),
+        py::arg("out"), py::arg("num_heads"), py::arg("v_dim"), py::arg("state_dim"), py::arg("groups"), py::arg("taps"),
+        py::arg("conv_off"), py::arg("step_off"));
+  m.def("conv_tail", &conv_tail, py::arg("x"), py::arg("state"), py::arg("tail_off"), py::arg("cu_q"),
+        py::arg("state_slots"), py::arg("conv_off"), py::arg("channels"), py::arg("taps"));
   m.def("scaled_sum", &scaled_sum, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("sa"), py::arg("sb"));
   m.def("moe_route", &moe_route, py::arg("logits"), py::arg("correction"), py::arg("chosen"), py::arg("weights"),
-        py::arg("groups"), py::arg("keep_groups"), py::arg("group_top"), py::arg("scale"), py::arg("weight_eps"));
+        py::arg("groups"), py::arg("keep_groups"), py::arg("group_top"), py::arg("scale"), py::arg("weight_eps"),
+        py::arg("score_kind") = 0);
   m.def("moe_router", &moe_router, py::arg("x"), py::arg("w"), py::arg("logits"));
   m.def("moe_sort", &moe_sort, py::arg("chosen"), py::arg("order"), py::arg("offsets"));
   m.def("moe_gate_up", &moe_gate_up, py::arg("x"), py::arg("w"), py::arg("order"), py::arg("offsets"), py::arg("act"),
-        py::arg("top"), py::arg("limit"), py::arg("slope"), py::arg("form") = 0);
+        py::arg("top"), py::arg("limit"), py::arg("slope"), py::arg("form") = 0, py::arg("up_offset") = 1.0);
   m.def("moe_down", &moe_down, py::arg("act"), py::arg("w"), py::arg("order"), py::arg("offsets"), py::arg("weights"),
         py::arg("out"), py::arg("form") = 0);
   m.def("moe_combine", &moe_combine, py::arg("parts"), py::arg("shared"), py::arg("out"), py::arg("top"));

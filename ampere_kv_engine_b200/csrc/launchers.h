@@ -346,6 +346,7 @@ struct MoeRouteParams {
   int64_t num_tokens;
   int experts, top, groups, keep_groups, group_top;
   float scale, weight_eps;
+  int score_kind;              // 0: sigmoid of each logit; 1: softmax over all experts
 };
 int launch_moe_route(const MoeRouteParams& p, cudaStream_t stream);
 // logits[t, e] = x[t, :] . w[e, :] in float, a warp per (token, expert): for steps of a few tokens.
@@ -364,6 +365,7 @@ struct MoeGemmParams {
   int64_t pairs;
   int experts, k, n, top;
   float limit, slope;
+  float up_offset;             // the gated product's activation is g sigmoid(slope g) (u + up_offset)
   int dtype;
   int force_plain;             // 0: the form is chosen by size; 1: float arithmetic; 2: mma.sync tiles; 3: few rows
 };
@@ -395,6 +397,9 @@ int launch_sample(const float* logits, const float* temperature, const float* un
 enum LinearScanMode : int {
   kGatedWrite = 0,      // a = f, k = 1 - f, f = lower + (1 - lower) sigmoid(x_k + gate_bias); q = silu(x_q); v = x_v
   kConstantDecay = 1,   // a = decay[head]; k = silu(x_k); q = silu(x_q); v = silu(x_v)
+  kPlainDecay = 2,      // a = decay[head]; q, k, v as they stand in x, which is float32 (prepared by another kernel)
+  kTokenDecay = 3,      // a = x[decay_off + head] of the token; q, k, v as they stand in x (float32); qk_group heads
+                        // in a row share a q and a k
 };
 constexpr int kLinearScanMaxDim = 256;
 struct LinearScanParams {
@@ -413,15 +418,40 @@ struct LinearScanParams {
   float* out;                  // [N, NH * DV] float32
   int64_t num_tokens;
   int num_seqs, num_heads, head_dim, v_dim, mode, dtype;
+  int qk_group;                // heads that share one q and one k (0 or 1: every head its own)
+  int decay_off;               // kTokenDecay: column of x where the token's decays (a float per head) begin
+  // filled in by the launcher: where the prompt form's staging warps find q, k and v in `act`
+  int64_t act_stride;
+  int act_q_off, act_k_off, act_v_off, act_aligned;
 };
 bool linear_scan_shape(int head_dim, int v_dim, int* rows, int* lanes);
 int64_t linear_scan_state_floats(int num_heads, int head_dim, int v_dim);
 int launch_linear_scan(const LinearScanParams& p, cudaStream_t stream);
-// out[t, c] = in[t, c] / sqrt(mean over c's group of `group` columns of in^2 + eps) * weight[c % weight_len] * factor
-// (* sigmoid(x[t, gate_off + c]) when x is given); in float32 [N, width], out in `dtype`.
-int launch_group_norm_gate(const float* in, void* out, const float* weight, int weight_len, int64_t num_tokens,
-                           int width, int group, float eps, float factor, const void* x, int64_t x_stride,
-                           int gate_off, int dtype, cudaStream_t stream);
+// v = in (+ skip_coef[c / skip_head] * skip[t, skip_off + c]) (* gate, if gate_first);
+// out[t, c] = v / sqrt(mean over c's group of `group` columns of v^2 + eps) * weight[c % weight_len] * factor
+// (* gate unless gate_first), gate = sigmoid or SiLU of x[t, gate_off + c] when x is given; in float32 [N, width],
+// out in `dtype`, x in `dtype`, skip float32.
+struct GroupNormGateParams {
+  const float* in;
+  void* out;
+  const float* weight;         // [weight_len] or null: no weight
+  int weight_len;
+  int64_t num_tokens;
+  int width, group;
+  float eps, factor;
+  const void* x;               // gate columns, or null
+  int64_t x_stride;
+  int gate_off;
+  int gate_kind;               // 0: sigmoid, 1: SiLU
+  int gate_first;              // 1: the gate multiplies before the norm
+  const float* skip;           // [N, skip_stride] or null
+  int64_t skip_stride;
+  int skip_off;
+  const float* skip_coef;      // a coefficient per run of skip_head columns
+  int skip_head;
+  int dtype;
+};
+int launch_group_norm_gate(const GroupNormGateParams& p, cudaStream_t stream);
 
 // Rotary positions on the q and k heads of one product, the value's preparation and the cache write (rotary_prep.cu).
 struct RotaryPrepParams {
@@ -441,10 +471,88 @@ struct RotaryPrepParams {
   int value_from_key;          // 1: the value is the key head before the turn
   int value_norm;              // 1: the value head is divided by sqrt(mean(v^2) + eps)
   float eps;
+  const float* q_norm;         // [NH * D] or null: q is divided by the root mean square of ALL its heads' entries (plus
+  const float* k_norm;         // row_norm_eps) and multiplied by this weight before the turn; [NKV * D] likewise for k
+  float row_norm_eps;
   int dtype;
   int* status;
 };
 int launch_rotary_prep(const RotaryPrepParams& p, cudaStream_t stream);
+
+// The q, k and v heads of one product as float32 rows [q | k | v] for a scan: the first rotary_dims dims of every q and
+// k head turned in the half layout (dim i with i + rotary_dims / 2), q times q_scale and k times k_scale afterwards.
+struct RotaryRowsParams {
+  const void* x;               // [N, x_stride], q from q_off (NH * D), k from k_off (NH * D), v from v_off (NH * DV)
+  int64_t x_stride;
+  int q_off, k_off, v_off;
+  const int32_t* positions;    // [N]
+  const float* freq;           // [rotary_dims / 2]
+  float* out;                  // [N, out_stride]: q at 0, k at NH * D, v at 2 * NH * D
+  int64_t out_stride;
+  int64_t num_tokens;
+  int num_heads, head_dim, v_dim, rotary_dims;
+  float q_scale, k_scale;
+  int dtype;
+};
+int launch_rotary_rows(const RotaryRowsParams& p, cudaStream_t stream);
+
+// Hyper-connections: a residual stream in `streams` copies per token (hyper_streams.cu).
+constexpr int kHyperMaxStreams = 8;
+struct HyperStepParams {
+  float* x;                    // [N, streams, width] float32
+  const void* y;               // [N, width] the sublayer's result to write back, or null
+  int y_dtype;
+  const float* mix;            // [streams, streams], from x to
+  const float* write;          // [streams]
+  const float* scale;          // [width] on y, or null
+  const float* read;           // [streams]: the next sublayer's mixture, with out
+  const float* weight;         // [width]: the norm's factor
+  float eps;
+  void* out;                   // [N or num_rows, width] the normed mixture in `dtype`, or null
+  const int32_t* rows;         // gather for out (then y must be null), or null
+  int64_t num_rows;
+  int64_t num_tokens;
+  int streams, width, dtype;
+  int* status;
+};
+int launch_hyper_step(const HyperStepParams& p, cudaStream_t stream);
+int launch_hyper_collapse(const HyperStepParams& p, float* sum, cudaStream_t stream);
+int launch_hyper_expand(const float* in, float* x, int64_t num_tokens, int streams, int width, cudaStream_t stream);
+int launch_normed_pair_sum(const float* a, const float* b, const float* wa, const float* wb, void* out,
+                           int64_t num_tokens, int width, float eps, float sa, float sb, int dtype, cudaStream_t stream);
+
+// A selective state-space mixer's preparation (state_space.cu).
+constexpr int kSsmMaxHeads = 1024;
+constexpr int kConvMaxTaps = 16;
+struct SsmPrepParams {
+  const void* x;               // [N, x_stride]: the convolved channels [x (H * P) | B (G * N) | C (G * N)] from conv_off,
+  int64_t x_stride;            // the step columns (H) from step_off
+  int conv_off, step_off;
+  const float* conv;           // [channels, taps]
+  const float* conv_bias;      // [channels] or null
+  const float* step_bias;      // [H]
+  const float* rate_log;       // [H]
+  const float* state;          // [slots, state_stride]; the convolutions' last taps - 1 inputs from tail_off
+  int64_t state_stride, tail_off;
+  const int32_t* cu_q;
+  const int32_t* state_slots;
+  float* out;                  // [N, out_stride]: [C | B | dt x | decay | x]
+  int64_t out_stride;
+  int64_t num_tokens;
+  int num_seqs, num_slots, num_heads, v_dim, state_dim, groups, taps, dtype;
+};
+int launch_ssm_prep(const SsmPrepParams& p, cudaStream_t stream);
+struct ConvTailParams {
+  const void* x;
+  int64_t x_stride;
+  int conv_off, channels, taps;
+  float* state;
+  int64_t state_stride, tail_off;
+  const int32_t* cu_q;
+  const int32_t* state_slots;
+  int num_seqs, num_slots, dtype;
+};
+int launch_conv_tail(const ConvTailParams& p, cudaStream_t stream);
 
 // hidden[t] += table[(previous token * mul_prev + token * mul_cur) mod buckets] (row `buckets` at position 0); the
 // token before a step's first row comes from, and the step's last token goes to, last_token[slot * state_stride]

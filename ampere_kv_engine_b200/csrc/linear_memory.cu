@@ -6,6 +6,10 @@
 //   kGatedWrite      a = f, k = 1 - f with f = lower + (1 - lower) * sigmoid(x_f + bias)  (a row keeps f of itself and
 //                    takes 1 - f of the value), q = silu(x_q), v = x_v
 //   kConstantDecay   a = decay[head] for every row, k = silu(x_k), q = silu(x_q), v = silu(x_v)
+//   kPlainDecay      a = decay[head]; q, k and v are taken as they are: a kernel before the scan has prepared them
+//                    (a rotation by position, a scale) and x is its float32 output
+//   kTokenDecay      a = x[decay_off + head] of the token (a scalar per head and token); q, k and v as they are;
+//                    qk_group heads in a row share one q and one k (a state-space mixer's groups)
 // Everything after the product is float32: gates, activations, the memory and both products with it.
 //
 // Work split: a block owns (sequence, head, 32 value columns) for the whole step; a thread holds ROWS rows of one
@@ -104,6 +108,8 @@ template <typename T, int MODE, int ROWS, int CHUNK, int PRODUCERS>
 __global__ void __launch_bounds__(256 + PRODUCERS)
 linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   constexpr int kRounds = scan_rounds(ROWS, PRODUCERS);
+  constexpr bool kPrepared = MODE == kPlainDecay || MODE == kTokenDecay;     // no activation, float32 input
+  constexpr int kExtra = MODE == kTokenDecay ? 4 : 0;                        // a token's decay, behind its v
   constexpr int kBatch = CHUNK < kScanBatch ? CHUNK : (ROWS >= 32 ? kScanBatch / 2 : kScanBatch);
   pdl_launch_dependents();
   pdl_wait();
@@ -129,7 +135,8 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   const int j = slice * kScanColumns + col;
   const int pitch = scan_pitch(ROWS, lanes);
   const int vec = lanes * pitch;                       // floats of a token's q (or a) in shared memory
-  const int per_token = 2 * vec + kScanColumns;        // [q | a | v]
+  const int per_token = 2 * vec + kScanColumns + kExtra;   // [q | a | v (| decay)]
+  const int qk_head = head / p.qk_group;               // whose q and k this head reads
   const int per_buffer = CHUNK * per_token;
 
   extern __shared__ __align__(16) float smem[];
@@ -141,7 +148,7 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) S[r] = mem[(int64_t)r * threads];
   }
-  const float decay = MODE == kConstantDecay ? p.decay[head] : 0.f;
+  const float decay = (MODE == kConstantDecay || MODE == kPlainDecay) ? p.decay[head] : 0.f;
 
   // What a staging thread stages of every token: entry i = stage_id + round * stagers of [q (D) | f or k (D) | v (the
   // slice's columns)].  Its column of x, its place in a token's shared-memory row and its gate constants are worked
@@ -149,7 +156,7 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   const int mine_cols = min(kScanColumns, DV - slice * kScanColumns);
   const int fetch_per_token = 2 * D + mine_cols;
   const T* src[kRounds];
-  int dst[kRounds], kind[kRounds];                     // kind 0: q, 1: f or k, 2: v
+  int dst[kRounds], kind[kRounds];                     // kind 0: q, 1: f or k, 2: v, 3: the token's decay
   float low[kRounds], bias[kRounds];
   const T* x = (const T*)p.x + (int64_t)t0 * p.x_stride;
 #pragma unroll
@@ -160,10 +167,10 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
     low[r] = bias[r] = 0.f;
     if (PRODUCERS == 0 && i < fetch_per_token) {
       if (i < D) {
-        src[r] = x + p.q_off + head * D + i;
+        src[r] = x + p.q_off + qk_head * D + i;
         dst[r] = i / ROWS * pitch + i % ROWS;
       } else if (i < 2 * D) {
-        const int d = i - D, ch = head * D + d;
+        const int d = i - D, ch = qk_head * D + d;
         src[r] = x + p.k_off + ch;
         dst[r] = vec + d / ROWS * pitch + d % ROWS;
         kind[r] = 1;
@@ -176,6 +183,10 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
         dst[r] = 2 * vec + (i - 2 * D);
         kind[r] = 2;
       }
+    } else if (PRODUCERS == 0 && MODE == kTokenDecay && i == fetch_per_token) {
+      src[r] = x + p.decay_off + head;
+      dst[r] = 2 * vec + kScanColumns;
+      kind[r] = 3;
     }
   }
   // tokens first .. first + count - 1 of the sequence into a buffer: kBatch tokens' loads at a time, then their
@@ -197,7 +208,8 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
           if (tb + t >= count) break;
           const float z = to_float<T>(raw[r][t]);
           float y;
-          if (kind[r] == 0) y = silu_f(z);
+          if (kPrepared) y = z;
+          else if (kind[r] == 0) y = silu_f(z);
           else if (kind[r] == 1) y = MODE == kGatedWrite ? low[r] + (1.f - low[r]) * sigmoid_f(z + bias[r]) : silu_f(z);
           else y = MODE == kGatedWrite ? z : silu_f(z);
           buffer[(tb + t) * per_token + dst[r]] = y;
@@ -208,8 +220,8 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   // the same from the scratch that the preparing kernel filled (prompt form): asynchronous copies of 16 bytes where
   // the widths allow it, of 4 otherwise, all of a chunk in flight at once
   auto stage_copy = [&](float* buffer, int first, int count) {
-    const int qk = H * D, width = 2 * qk + H * DV;
-    const bool wide_copy = D % 4 == 0 && DV % 4 == 0;
+    const int64_t width = p.act_stride;
+    const bool wide_copy = D % 4 == 0 && DV % 4 == 0 && p.act_aligned;
     const int step = wide_copy ? 4 : 1;
     const int per = fetch_per_token / step;
     const float* base = p.act + (int64_t)(t0 + first) * width;
@@ -218,22 +230,26 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
       const float* from = base + (int64_t)t * width;
       float* to = buffer + t * per_token;
       if (i < D) {
-        from += head * D + i;
+        from += p.act_q_off + qk_head * D + i;
         to += i / ROWS * pitch + i % ROWS;
       } else if (i < 2 * D) {
-        from += qk + head * D + (i - D);
+        from += p.act_k_off + qk_head * D + (i - D);
         to += vec + (i - D) / ROWS * pitch + (i - D) % ROWS;
       } else {
-        from += 2 * qk + head * DV + slice * kScanColumns + (i - 2 * D);
+        from += p.act_v_off + head * DV + slice * kScanColumns + (i - 2 * D);
         to += 2 * vec + (i - 2 * D);
       }
       if (wide_copy) cp_async_16(to, from);
       else cp_async_4(to, from);
     }
+    if (MODE == kTokenDecay) {
+      for (int t = stage_id; t < count; t += stagers)
+        cp_async_4(buffer + t * per_token + 2 * vec + kScanColumns, base + (int64_t)t * width + p.decay_off + head);
+    }
     cp_async_wait_all();
   };
   // a token's q, a and v applied to this thread's rows of S; returns its part of the token's output
-  auto apply_loaded = [&](const float4 (&qs)[ROWS / 4], const float4 (&as)[ROWS / 4], float v) -> float {
+  auto apply_loaded = [&](const float4 (&qs)[ROWS / 4], const float4 (&as)[ROWS / 4], float v, float decay) -> float {
     float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
     for (int r4 = 0; r4 < ROWS / 4; ++r4) {
@@ -259,8 +275,9 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
     return (o0 + o1) + (o2 + o3);
   };
   // a token's row of [q | a | v] in shared memory into registers
-  auto fetch = [&](const float* row, float4 (&qs)[ROWS / 4], float4 (&as)[ROWS / 4], float& v) {
+  auto fetch = [&](const float* row, float4 (&qs)[ROWS / 4], float4 (&as)[ROWS / 4], float& v, float& d) {
     v = row[2 * vec + col];
+    if (MODE == kTokenDecay) d = row[2 * vec + kScanColumns];
     const float4* q4 = reinterpret_cast<const float4*>(row + sub * pitch);
     const float4* a4 = reinterpret_cast<const float4*>(row + vec + sub * pitch);
 #pragma unroll
@@ -271,9 +288,9 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   };
   auto apply = [&](const float* row) -> float {
     float4 qs[ROWS / 4], as[ROWS / 4];
-    float v;
-    fetch(row, qs, as, v);
-    return apply_loaded(qs, as, v);
+    float v, d = decay;
+    fetch(row, qs, as, v, d);
+    return apply_loaded(qs, as, v, d);
   };
   const int wide = H * DV;
   // count tokens of a buffer in their order, decode form: the lanes that share a column add up their parts of a
@@ -350,28 +367,44 @@ linear_scan_kernel(LinearScanParams p, int lanes, int slices) {
   }
 }
 
-// out[t, c] = in[t, c] / sqrt(mean over c's group of in^2 + eps) * weight[c % weight_len] * factor
-//             (* sigmoid(x[t, gate_off + c]));   one block per (token, group)
+// v[t, c]   = in[t, c] (+ skip_coef[c / skip_head] * skip[t, skip_off + c])  (* gate(x[t, gate_off + c]), gate_first)
+// out[t, c] = v / sqrt(mean over c's group of v^2 + eps) * weight[c % weight_len] * factor
+//             (* gate(x[t, gate_off + c]), unless gate_first);   gate: sigmoid or SiLU;   one block per (token, group)
 template <typename T>
-__global__ void group_norm_gate_kernel(const float* __restrict__ in, T* __restrict__ out, const float* __restrict__ weight,
-                                       int weight_len, int group, int width, float eps, float factor,
-                                       const T* __restrict__ x, int64_t x_stride, int gate_off) {
+__global__ void group_norm_gate_kernel(GroupNormGateParams p) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
+  const int group = p.group, width = p.width;
   const int groups = width / group;
   const int64_t token = blockIdx.x / groups;
   const int g = blockIdx.x % groups;
-  const float* src = in + token * width + (int64_t)g * group;
+  const float* src = p.in + token * width + (int64_t)g * group;
+  const T* x = (const T*)p.x;
+  auto gate = [&](int c) -> float {
+    const float z = to_float<T>(x[token * p.x_stride + p.gate_off + c]);
+    return p.gate_kind == 1 ? silu_f(z) : sigmoid_f(z);
+  };
+  auto value = [&](int i) -> float {
+    const int c = g * group + i;
+    float v = src[i];
+    if (p.skip != nullptr) v = fmaf(p.skip_coef[c / p.skip_head], p.skip[token * p.skip_stride + p.skip_off + c], v);
+    if (x != nullptr && p.gate_first) v *= gate(c);
+    return v;
+  };
   float ss = 0.f;
-  for (int i = threadIdx.x; i < group; i += blockDim.x) ss += src[i] * src[i];
+  for (int i = threadIdx.x; i < group; i += blockDim.x) {
+    const float v = value(i);
+    ss = fmaf(v, v, ss);
+  }
   ss = block_sum(ss, scratch);
-  const float inv = factor / sqrtf(ss / (float)group + eps);
-  T* dst = out + token * width + (int64_t)g * group;
+  const float inv = p.factor / sqrtf(ss / (float)group + p.eps);
+  T* dst = (T*)p.out + token * width + (int64_t)g * group;
   for (int i = threadIdx.x; i < group; i += blockDim.x) {
     const int c = g * group + i;
-    float y = src[i] * inv * weight[c % weight_len];
-    if (x != nullptr) y *= sigmoid_f(to_float<T>(x[token * x_stride + gate_off + c]));
+    float y = value(i) * inv;
+    if (p.weight != nullptr) y *= p.weight[c % p.weight_len];
+    if (x != nullptr && !p.gate_first) y *= gate(c);
     dst[i] = from_float<T>(y);
   }
 }
@@ -401,9 +434,10 @@ static int launch_scan_chunk(const LinearScanParams& p, int lanes, cudaStream_t 
   const int slices = (p.v_dim + kScanColumns - 1) / kScanColumns;
   const int64_t blocks = (int64_t)p.num_seqs * p.num_heads * slices;
   const int stagers = PRODUCERS > 0 ? PRODUCERS : kScanColumns * lanes;
-  if (blocks > 0x7fffffffLL || 2 * p.head_dim + kScanColumns > scan_rounds(ROWS, PRODUCERS) * stagers)
+  if (blocks > 0x7fffffffLL || 2 * p.head_dim + kScanColumns + 1 > scan_rounds(ROWS, PRODUCERS) * stagers)
     return (int)cudaErrorInvalidValue;
-  const size_t smem = (2 * (size_t)CHUNK * (2 * lanes * scan_pitch(ROWS, lanes) + kScanColumns) +
+  const size_t smem = (2 * (size_t)CHUNK * (2 * lanes * scan_pitch(ROWS, lanes) + kScanColumns +
+                                            (MODE == kTokenDecay ? 4 : 0)) +
                        (PRODUCERS > 0 ? (size_t)CHUNK * lanes * kScanColumns : 0)) * sizeof(float);
   auto kernel = linear_scan_kernel<T, MODE, ROWS, CHUNK, PRODUCERS>;
   if (smem > 48 * 1024) {
@@ -421,12 +455,14 @@ static int launch_scan_chunk(const LinearScanParams& p, int lanes, cudaStream_t 
 template <typename T, int MODE, int ROWS>
 static int launch_scan(const LinearScanParams& p, int lanes, cudaStream_t stream) {
   if (p.act == nullptr) return launch_scan_chunk<T, MODE, ROWS, 2, 0>(p, lanes, stream);
-  const int width = 2 * p.num_heads * p.head_dim + p.num_heads * p.v_dim;
   if (p.num_tokens > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
-  const int across = std::min((width + 255) / 256, 64);
-  const int err = (int)launch_chain(linear_prep_kernel<T, MODE>, dim3((unsigned)p.num_tokens, (unsigned)across),
-                                    dim3(256), 0, stream, dim3(1, 1, 1), p, width);
-  if (err != 0) return err;
+  if constexpr (MODE == kGatedWrite || MODE == kConstantDecay) {
+    const int width = 2 * p.num_heads * p.head_dim + p.num_heads * p.v_dim;
+    const int across = std::min((width + 255) / 256, 64);
+    const int err = (int)launch_chain(linear_prep_kernel<T, MODE>, dim3((unsigned)p.num_tokens, (unsigned)across),
+                                      dim3(256), 0, stream, dim3(1, 1, 1), p, width);
+    if (err != 0) return err;
+  }
   return launch_scan_chunk<T, MODE, ROWS, (ROWS >= 32 ? 8 : 32), kScanProducers>(p, lanes, stream);
 }
 
@@ -438,32 +474,60 @@ static int launch_scan_typed(const LinearScanParams& p, int rows, int lanes, cud
                     : launch_scan<T, kConstantDecay, 32>(p, lanes, stream);
 }
 
-int launch_linear_scan(const LinearScanParams& p, cudaStream_t stream) {
+int launch_linear_scan(const LinearScanParams& given, cudaStream_t stream) {
+  LinearScanParams p = given;
   if (p.num_tokens == 0 || p.num_seqs == 0) return 0;
+  if (p.qk_group == 0) p.qk_group = 1;
+  // where the staging warps of the prompt form find a token's q, k and v: in the scratch of the preparing kernel, or,
+  // for the prepared modes, in x itself
+  if (p.mode == kPlainDecay || p.mode == kTokenDecay) {
+    p.act_stride = p.x_stride;
+    p.act_q_off = p.q_off;
+    p.act_k_off = p.k_off;
+    p.act_v_off = p.v_off;
+    p.act_aligned = (p.x_stride % 4 == 0 && p.q_off % 4 == 0 && p.k_off % 4 == 0 && p.v_off % 4 == 0 &&
+                     reinterpret_cast<uintptr_t>(p.x) % 16 == 0) ? 1 : 0;
+  } else {
+    const int qk = p.num_heads * p.head_dim;
+    p.act_stride = 2 * (int64_t)qk + (int64_t)p.num_heads * p.v_dim;
+    p.act_q_off = 0;
+    p.act_k_off = qk;
+    p.act_v_off = 2 * qk;
+    p.act_aligned = 1;
+  }
   int rows = 0, lanes = 0;
-  if (!linear_scan_shape(p.head_dim, p.v_dim, &rows, &lanes) || p.num_heads < 1 ||
-      (p.mode != kGatedWrite && p.mode != kConstantDecay))
+  if (!linear_scan_shape(p.head_dim, p.v_dim, &rows, &lanes) || p.num_heads < 1 || p.mode < kGatedWrite ||
+      p.mode > kTokenDecay || p.qk_group < 1 || p.num_heads % p.qk_group)
     return (int)cudaErrorInvalidValue;
-  if (p.mode == kGatedWrite ? p.lower == nullptr : p.decay == nullptr) return (int)cudaErrorInvalidValue;
+  if (p.mode == kGatedWrite ? p.lower == nullptr : (p.mode != kTokenDecay && p.decay == nullptr))
+    return (int)cudaErrorInvalidValue;
+  if (p.mode == kPlainDecay || p.mode == kTokenDecay) {
+    // prepared input: float32 rows that the staging warps copy from as they are
+    if (p.dtype != kFloat32 || (p.act != nullptr && p.act != (const float*)p.x)) return (int)cudaErrorInvalidValue;
+    if (p.mode == kPlainDecay)
+      return rows == 16 ? launch_scan<float, kPlainDecay, 16>(p, lanes, stream)
+                        : launch_scan<float, kPlainDecay, 32>(p, lanes, stream);
+    return rows == 16 ? launch_scan<float, kTokenDecay, 16>(p, lanes, stream)
+                      : launch_scan<float, kTokenDecay, 32>(p, lanes, stream);
+  }
+  if (p.qk_group != 1) return (int)cudaErrorInvalidValue;
   return p.dtype == kBFloat16 ? launch_scan_typed<__nv_bfloat16>(p, rows, lanes, stream)
                               : launch_scan_typed<float>(p, rows, lanes, stream);
 }
 
-int launch_group_norm_gate(const float* in, void* out, const float* weight, int weight_len, int64_t num_tokens,
-                           int width, int group, float eps, float factor, const void* x, int64_t x_stride,
-                           int gate_off, int dtype, cudaStream_t stream) {
-  if (num_tokens == 0) return 0;
-  if (group < 1 || width % group || weight_len < 1) return (int)cudaErrorInvalidValue;
-  const int64_t blocks = num_tokens * (width / group);
+int launch_group_norm_gate(const GroupNormGateParams& p, cudaStream_t stream) {
+  if (p.num_tokens == 0) return 0;
+  if (p.group < 1 || p.width % p.group || (p.weight != nullptr && p.weight_len < 1) ||
+      (p.skip != nullptr && (p.skip_coef == nullptr || p.skip_head < 1)))
+    return (int)cudaErrorInvalidValue;
+  const int64_t blocks = p.num_tokens * (p.width / p.group);
   if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  const int group = p.group;
   const int threads = group >= 1024 ? 256 : (group >= 128 ? 128 : (group > 32 ? 64 : 32));
-  if (dtype == kBFloat16)
+  if (p.dtype == kBFloat16)
     return (int)launch_chain(group_norm_gate_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream,
-                             dim3(1, 1, 1), in, (__nv_bfloat16*)out, weight, weight_len, group, width, eps, factor,
-                             (const __nv_bfloat16*)x, x_stride, gate_off);
-  return (int)launch_chain(group_norm_gate_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, dim3(1, 1, 1),
-                           in, (float*)out, weight, weight_len, group, width, eps, factor, (const float*)x, x_stride,
-                           gate_off);
+                             dim3(1, 1, 1), p);
+  return (int)launch_chain(group_norm_gate_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, dim3(1, 1, 1), p);
 }
 
 }  // namespace akv

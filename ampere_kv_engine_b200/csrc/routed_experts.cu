@@ -46,8 +46,20 @@ __global__ void moe_route_kernel(MoeRouteParams p) {
   float* group_score = choice + E;
   float* group_kept = group_score + groups;
   const float* z = p.logits + token * E;
+  // softmax scores: the row's maximum and the sum of the exponentials first (a row of padding may hold anything)
+  float row_max = 0.f, row_inv = 1.f;
+  if (p.score_kind == 1) {
+    float m = -FLT_MAX;
+    for (int e = lane; e < E; e += 32)
+      if (z[e] == z[e]) m = fmaxf(m, fminf(z[e], FLT_MAX));
+    row_max = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(z[e] - row_max);
+    sum = warp_sum(sum);
+    row_inv = 1.f / sum;
+  }
   for (int e = lane; e < E; e += 32) {
-    const float s = 1.f / (1.f + expf(-z[e]));
+    const float s = p.score_kind == 1 ? expf(z[e] - row_max) * row_inv : 1.f / (1.f + expf(-z[e]));
     float c = p.correction != nullptr ? s + p.correction[e] : s;
     if (!(c == c)) c = -FLT_MAX;          // a row of padding may hold anything; the choice must still be an expert
     score[e] = s;
@@ -187,7 +199,8 @@ int launch_moe_router(const void* x, const void* w, float* logits, int64_t token
 int launch_moe_route(const MoeRouteParams& p, cudaStream_t stream) {
   if (p.num_tokens == 0) return 0;
   if (p.experts <= 0 || p.experts > kMoeMaxExperts || p.top <= 0 || p.top > 32 || p.top > p.experts || p.groups <= 0 ||
-      p.experts % p.groups || p.keep_groups <= 0 || p.keep_groups > p.groups || p.group_top <= 0)
+      p.experts % p.groups || p.keep_groups <= 0 || p.keep_groups > p.groups || p.group_top <= 0 ||
+      (p.score_kind != 0 && p.score_kind != 1))
     return (int)cudaErrorInvalidValue;
   const size_t smem = (size_t)kRouteWarps * (2 * p.experts + 2 * p.groups) * sizeof(float);
   const int64_t blocks = (p.num_tokens + kRouteWarps - 1) / kRouteWarps;
@@ -333,7 +346,7 @@ __global__ void __launch_bounds__(kGemmThreads) moe_gemm_kernel(MoeGemmParams p)
         if (c >= N) continue;
         const float g = fminf(acc[0][i][j], p.limit);
         const float u = fminf(fmaxf(acc[GATED ? 1 : 0][i][j], -p.limit), p.limit);
-        dst[c] = from_float<T>(g / (1.f + expf(-p.slope * g)) * (u + 1.f));
+        dst[c] = from_float<T>(g / (1.f + expf(-p.slope * g)) * (u + p.up_offset));
       }
     } else {
       const int pair = p.order[row0 + r];
@@ -524,7 +537,7 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(MoeGemmParams p) {
             if (c >= N) continue;
             const float g = fminf(acc[i][j][half * 2 + e], p.limit);
             const float u = fminf(fmaxf(acc[i][j + 2][half * 2 + e], -p.limit), p.limit);
-            dst[c] = __float2bfloat16_rn(g / (1.f + expf(-p.slope * g)) * (u + 1.f));
+            dst[c] = __float2bfloat16_rn(g / (1.f + expf(-p.slope * g)) * (u + p.up_offset));
           }
         }
       } else {
@@ -645,7 +658,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) moe_gemv_kernel(MoeGemmParams
           const float g = fminf(first, p.limit);
           const float u = fminf(fmaxf(second, -p.limit), p.limit);
           ((__nv_bfloat16*)p.out)[(int64_t)(begin + r0 + lane) * N + feature] =
-              __float2bfloat16_rn(g / (1.f + expf(-p.slope * g)) * (u + 1.f));
+              __float2bfloat16_rn(g / (1.f + expf(-p.slope * g)) * (u + p.up_offset));
         } else {
           int mine = pair[0];
 #pragma unroll

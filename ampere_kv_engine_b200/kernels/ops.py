@@ -543,8 +543,12 @@ def moe_router_logits(x, w_router, status=None):
     return linear(x, w_router, out_dtype=torch.float32, status=status)
 
 
-def moe_route(logits, correction, *, top, groups, keep_groups, group_top, scale, weight_eps):
-    """Scores ``sigmoid(logits)`` (float32 [tokens, experts]); choice scores are the scores plus ``correction``
+MOE_SCORES = {"sigmoid": 0, "softmax": 1}
+
+
+def moe_route(logits, correction, *, top, groups, keep_groups, group_top, scale, weight_eps, score: str = "sigmoid"):
+    """Scores ``sigmoid(logits)``, or with ``score="softmax"`` the softmax over all experts (float32
+    [tokens, experts]); choice scores are the scores plus ``correction``
     (float32 [experts] or None); experts form ``groups`` equal runs, a group's score is the sum of its ``group_top``
     largest choice scores, experts outside the ``keep_groups`` best groups cannot be chosen; the ``top`` largest
     remaining choice scores are chosen (ties: the lower index).  Returns (int32 [tokens, top], float32 [tokens, top]:
@@ -552,7 +556,8 @@ def moe_route(logits, correction, *, top, groups, keep_groups, group_top, scale,
     n = logits.shape[0]
     chosen = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((n, top), dtype=torch.float32, device=logits.device)
-    ext().moe_route(logits, correction, chosen, weights, groups, keep_groups, group_top, float(scale), float(weight_eps))
+    ext().moe_route(logits, correction, chosen, weights, groups, keep_groups, group_top, float(scale), float(weight_eps),
+                    MOE_SCORES[score])
     _launched()
     return chosen, weights
 
@@ -567,9 +572,10 @@ def moe_sort(chosen, experts: int):
     return order, offsets
 
 
-def moe_gate_up(x, w_gate_up, order, offsets, *, top, limit, slope, kernel: str = "auto"):
-    """Row r of the result belongs to pair ``order[r]`` and is its expert's ``g * sigmoid(slope * g) * (u + 1)`` with
-    ``g = min(W_gate x, limit)``, ``u = clamp(W_up x, -limit, limit)`` for the pair's token;
+def moe_gate_up(x, w_gate_up, order, offsets, *, top, limit, slope, kernel: str = "auto", up_offset: float = 1.0):
+    """Row r of the result belongs to pair ``order[r]`` and is its expert's ``g * sigmoid(slope * g) * (u + up_offset)``
+    with ``g = min(W_gate x, limit)``, ``u = clamp(W_up x, -limit, limit)`` for the pair's token (an infinite limit, a
+    slope of one and no offset make it ``silu(g) * u``);
     ``w_gate_up`` [experts, gate rows then up rows, hidden].  [tokens * top, intermediate] in the dtype of ``x``.
     ``kernel``: ``"auto"``: for bfloat16 with a hidden size that is a multiple of eight, the few-rows form (weights
     streamed once, no staging) for the gated product of steps of up to 128 pairs and the tensor cores (``mma.sync``
@@ -577,7 +583,8 @@ def moe_gate_up(x, w_gate_up, order, offsets, *, top, limit, slope, kernel: str 
     ``"plain"`` keeps the float-arithmetic form, which is also all of float32; ``"mma"`` / ``"few"`` force one."""
     inter = w_gate_up.shape[1] // 2
     act = torch.empty((order.numel(), inter), dtype=x.dtype, device=x.device)
-    ext().moe_gate_up(x, w_gate_up, order, offsets, act, top, float(limit), float(slope), MOE_FORMS[kernel])
+    ext().moe_gate_up(x, w_gate_up, order, offsets, act, top, float(limit), float(slope), MOE_FORMS[kernel],
+                      float(up_offset))
     _launched()
     return act
 
@@ -956,24 +963,40 @@ ROTARY_LAYOUTS = {"half": 0, "pairs": 1}
 
 def rotary_prep(x, positions, slots, freq, k_cache, v_cache, *, num_heads, num_kv_heads, head_dim, v_dim, rotary_dims,
                 layout: str, factor: float = 1.0, value_from_key: bool = False, value_norm: bool = False,
-                eps: float = 0.0, status=None) -> torch.Tensor:
+                eps: float = 0.0, status=None, q_norm=None, k_norm=None, row_norm_eps: float = 0.0) -> torch.Tensor:
     """From one product ``x`` [tokens, q heads | k heads (| v heads)]: the first ``rotary_dims`` dims of every q and k
     head turned by ``positions[t] * freq[i]`` (``layout`` ``"half"``: dim i pairs with i + rotary_dims / 2;
     ``"pairs"``: dim 2i with 2i + 1; cos and sin times ``factor``); the value is the v head (divided by its root mean
     square with ``value_norm``), or with ``value_from_key`` the k head before the turn (no v columns then); k and v go
-    to their cache slots.  Returns q [tokens, heads * head_dim]."""
+    to their cache slots.  With ``q_norm`` / ``k_norm`` (float32 [heads * head_dim] / [kv heads * head_dim]) the whole q
+    row and the whole k row are first divided by their root mean square over all heads (``row_norm_eps`` inside the
+    root) and multiplied by these weights.  Returns q [tokens, heads * head_dim]."""
     q_out = torch.empty((x.shape[0], num_heads * head_dim), dtype=x.dtype, device=x.device)
     ext().rotary_prep(x, positions, slots, freq, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim, v_dim,
                       int(rotary_dims), ROTARY_LAYOUTS[layout], float(factor), bool(value_from_key), bool(value_norm),
-                      float(eps), status)
+                      float(eps), status, q_norm, k_norm, float(row_norm_eps))
     _launched()
     return q_out
+
+
+def rotary_rows(x, positions, freq, *, num_heads, head_dim, v_dim, rotary_dims, q_off: int, k_off: int, v_off: int,
+                q_scale: float = 1.0, k_scale: float = 1.0) -> torch.Tensor:
+    """The q, k and v heads of one product as float32 rows ``[q | k | v]`` (padded to a multiple of four floats) for a
+    scan that keeps everything in float32: the first ``rotary_dims`` dims of every q and k head turned by
+    ``positions[t] * freq[i]`` (dim i pairs with i + rotary_dims / 2), then q times ``q_scale`` and k times
+    ``k_scale``."""
+    width = 2 * num_heads * head_dim + num_heads * v_dim
+    out = torch.empty((x.shape[0], (width + 3) // 4 * 4), dtype=torch.float32, device=x.device)
+    ext().rotary_rows(x, positions, freq, out, num_heads, head_dim, v_dim, int(rotary_dims), int(q_off), int(k_off),
+                      int(v_off), float(q_scale), float(k_scale))
+    _launched()
+    return out
 
 
 # ----------------------------------------------------------------------------- linear attention with a decaying memory
 
 LINEAR_SCAN_MAX_DIM = 256
-LINEAR_SCAN_MODES = {"gated_write": 0, "constant_decay": 1}
+LINEAR_SCAN_MODES = {"gated_write": 0, "constant_decay": 1, "plain_decay": 2, "token_decay": 3}
 _SCAN_COLUMNS = 32
 
 
@@ -1006,24 +1029,133 @@ def linear_scan_memory(state_row: torch.Tensor, num_heads: int, head_dim: int, v
 
 
 def linear_scan(x, state, cu_q, state_slots, *, num_heads, head_dim, v_dim, mode: str, q_off: int, k_off: int,
-                v_off: int, gate_bias=None, lower=None, decay=None) -> torch.Tensor:
+                v_off: int, gate_bias=None, lower=None, decay=None, qk_group: int = 1, decay_off: int = 0) -> torch.Tensor:
     """``S_t = diag(a_t) S_(t-1) + k_t v_t^T; o_t = S_t^T q_t`` per head over the step's tokens, sequence by sequence,
     from and into ``state`` [slots, floats] float32 (:func:`linear_scan_state_floats` of them per slot).  The columns
     of ``x`` from ``q_off`` / ``k_off`` / ``v_off`` hold a product's q, gate-or-key and v.  ``mode`` ``"gated_write"``:
     ``a = f, k = 1 - f`` with ``f = lower + (1 - lower) sigmoid(x_k + gate_bias)``, ``q = silu(x_q)``, ``v = x_v``;
-    ``"constant_decay"``: ``a = decay[head]``, q, k and v through SiLU.  Returns float32 [tokens, heads * v_dim]."""
+    ``"constant_decay"``: ``a = decay[head]``, q, k and v through SiLU; ``"plain_decay"``: ``a = decay[head]`` and q,
+    k, v as they stand in ``x``, which is then float32 (a kernel before has prepared them); ``"token_decay"``: the
+    same with ``a = x[t, decay_off + head]``, a scalar per head and token, and ``qk_group`` heads in a row sharing one
+    q and one k (the q and k columns then hold ``num_heads / qk_group`` heads).  Returns float32
+    [tokens, heads * v_dim]."""
     out = torch.empty((x.shape[0], num_heads * v_dim), dtype=torch.float32, device=x.device)
     ext().linear_scan(x, state, cu_q, state_slots, out, num_heads, head_dim, v_dim, LINEAR_SCAN_MODES[mode], int(q_off),
-                      int(k_off), int(v_off), gate_bias, lower, decay)
+                      int(k_off), int(v_off), gate_bias, lower, decay, int(qk_group), int(decay_off))
     _launched()
     return out
 
 
-def group_norm_gate(o, weight, *, group: int, eps: float, out_dtype, factor: float = 1.0, x=None, gate_off: int = 0):
-    """``o / sqrt(mean over each group of `group` columns of o^2 + eps) * weight * factor`` (``weight`` holds a
-    group's or the whole width's entries), times ``sigmoid(x[:, gate_off + column])`` when ``x`` is given; ``o``
-    float32 [tokens, width], the result in ``out_dtype``."""
+GATE_KINDS = {"sigmoid": 0, "silu": 1}
+
+
+def group_norm_gate(o, weight, *, group: int, eps: float, out_dtype, factor: float = 1.0, x=None, gate_off: int = 0,
+                    gate: str = "sigmoid", gate_first: bool = False, skip=None, skip_off: int = 0, skip_coef=None,
+                    skip_head: int = 1):
+    """``v / sqrt(mean over each group of `group` columns of v^2 + eps) * weight * factor`` (``weight`` holds a
+    group's or the whole width's entries, or is None), where ``v`` is ``o`` (float32 [tokens, width]), plus
+    ``skip_coef[column // skip_head] * skip[:, skip_off + column]`` when ``skip`` (float32) is given.  With ``x`` the
+    result is gated by ``sigmoid`` or ``silu`` (``gate``) of ``x[:, gate_off + column]``: after the norm, or with
+    ``gate_first`` before it (the gate then enters the root mean square).  The result is in ``out_dtype``."""
     out = torch.empty(o.shape, dtype=out_dtype, device=o.device)
-    ext().group_norm_gate(o, out, weight, int(group), float(eps), float(factor), x, int(gate_off))
+    ext().group_norm_gate(o, out, weight, int(group), float(eps), float(factor), x, int(gate_off), GATE_KINDS[gate],
+                          bool(gate_first), skip, int(skip_off), skip_coef, int(skip_head))
+    _launched()
+    return out
+
+
+# ----------------------------------------------------------------------------- a selective state-space mixer
+
+SSM_MAX_HEADS = 1024
+CONV_MAX_TAPS = 16
+
+
+def ssm_prep_width(num_heads: int, v_dim: int, state_dim: int, groups: int) -> int:
+    """Floats of a token's prepared row ``[C | B | dt x | decay | x]``, rounded up to a multiple of four."""
+    return (2 * groups * state_dim + 2 * num_heads * v_dim + num_heads + 3) // 4 * 4
+
+
+def ssm_prep(x, conv, conv_bias, step_bias, rate_log, state, cu_q, state_slots, *, tail_off: int, num_heads, v_dim,
+             state_dim, groups, taps, conv_off: int, step_off: int) -> torch.Tensor:
+    """From one product ``x`` whose columns from ``conv_off`` hold ``[x (heads * v_dim) | B (groups * state_dim) |
+    C (groups * state_dim)]`` and from ``step_off`` a step per head: the channels through their causal convolution
+    over the sequence's own earlier tokens (``conv`` float32 [channels, taps], last tap the current token's, plus
+    ``conv_bias``; before the step's first token the inputs come from ``state[slot, tail_off:]``) and SiLU;
+    ``dt = softplus(step + step_bias)``, ``decay = exp(-exp(rate_log) * dt)``.  Returns float32 rows
+    ``[C | B | dt * x | decay | x]``: q, k, v and the per-token decay of ``linear_scan(mode="token_decay")``, and the
+    skip input.  The state is not changed."""
+    out = torch.empty((x.shape[0], ssm_prep_width(num_heads, v_dim, state_dim, groups)), dtype=torch.float32,
+                      device=x.device)
+    ext().ssm_prep(x, conv, conv_bias, step_bias, rate_log, state, int(tail_off), cu_q, state_slots, out, num_heads,
+                   v_dim, state_dim, groups, taps, int(conv_off), int(step_off))
+    _launched()
+    return out
+
+
+def conv_tail(x, state, cu_q, state_slots, *, tail_off: int, conv_off: int, channels: int, taps: int) -> None:
+    """Every sequence's last ``taps - 1`` rows of the columns ``[conv_off, conv_off + channels)`` of ``x`` (older rows
+    from what the slot held) into ``state[slot, tail_off:]`` as [taps - 1, channels]."""
+    if taps <= 1:
+        return
+    ext().conv_tail(x, state, int(tail_off), cu_q, state_slots, int(conv_off), int(channels), int(taps))
+    _launched()
+
+
+# ----------------------------------------------------------------------------- a residual stream in several copies
+
+HYPER_MAX_STREAMS = 8
+
+
+class HyperPending:
+    """A sublayer's result that is not yet written back into the copies of the stream: ``y`` [tokens, width] with the
+    coefficients of its write (``mix`` [streams, streams] from -> to, ``write`` [streams], ``scale`` [width] or None)."""
+
+    def __init__(self, y: torch.Tensor, mix: torch.Tensor, write: torch.Tensor, scale: torch.Tensor | None):
+        self.y, self.mix, self.write, self.scale = y, mix, write, scale
+
+
+def hyper_expand(hidden: torch.Tensor, streams: int) -> torch.Tensor:
+    """``streams`` copies of every row: float32 [tokens, width] -> [tokens, streams, width]."""
+    x = torch.empty((hidden.shape[0], streams, hidden.shape[1]), dtype=torch.float32, device=hidden.device)
+    ext().hyper_expand(hidden, x)
+    _launched()
+    return x
+
+
+def hyper_step(x: torch.Tensor, pending: HyperPending | None, read: torch.Tensor | None, weight: torch.Tensor | None,
+               eps: float, out_dtype, rows: torch.Tensor | None = None, status=None) -> torch.Tensor | None:
+    """One pass over the copies ``x`` [tokens, streams, width] (float32, changed in place): the pending write
+    ``x_t <- sum_s mix[s, t] x_s + write[t] * scale * y`` if there is one, then, if ``read`` is given, the next
+    sublayer's input ``u = sum_s read[s] x_s`` normed: ``u / sqrt(mean(u^2) + eps) * weight`` in ``out_dtype``
+    (only the rows ``rows`` when given; a gather goes without a write)."""
+    out = None
+    if read is not None:
+        n = rows.numel() if rows is not None else x.shape[0]
+        out = torch.empty((n, x.shape[2]), dtype=out_dtype, device=x.device)
+    if pending is None:
+        ext().hyper_step(x, None, None, None, None, read, weight, float(eps), out, rows, status)
+    else:
+        ext().hyper_step(x, pending.y, pending.mix, pending.write, pending.scale, read, weight, float(eps), out, rows,
+                         status)
+    _launched()
+    return out
+
+
+def hyper_collapse(x: torch.Tensor, pending: HyperPending | None) -> torch.Tensor:
+    """The sum of the copies after the pending write (which is not stored): float32 [tokens, width]."""
+    out = torch.empty((x.shape[0], x.shape[2]), dtype=torch.float32, device=x.device)
+    if pending is None:
+        ext().hyper_collapse(x, None, None, None, None, out)
+    else:
+        ext().hyper_collapse(x, pending.y, pending.mix, pending.write, pending.scale, out)
+    _launched()
+    return out
+
+
+def normed_pair_sum(a, b, wa, wb, *, eps: float, sa: float, sb: float, out_dtype) -> torch.Tensor:
+    """``sa * a / sqrt(mean(a^2) + eps) * wa + sb * b / sqrt(mean(b^2) + eps) * wb`` row by row; ``a`` and ``b``
+    float32 [tokens, width], the result in ``out_dtype``."""
+    out = torch.empty(a.shape, dtype=out_dtype, device=a.device)
+    ext().normed_pair_sum(a, b, wa, wb, out, float(eps), float(sa), float(sb))
     _launched()
     return out

@@ -13,9 +13,9 @@ import torch
 
 from ..config.spec import ModelSpec
 from ..kernels import ops
-from ..parts import (attention, block, embedding, feed_forward, gated_delta, latent_attention,  # noqa: F401
+from ..parts import (attention, block, embedding, feed_forward, gated_delta, hyper, latent_attention,  # noqa: F401
                      linear_memory, norm, parallel, position, rotary_attention, routed_experts,
-                     scored_attention)                          # (importing them registers the built-in kinds)
+                     scored_attention, state_space)             # (importing them registers the built-in kinds)
 from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, Block, CacheSpec, ParamSpec, build_part
 
 
@@ -117,11 +117,16 @@ class DecoderModel:
         # a schedule that sends the stream through layers again adds the embedding's output before each such pass
         start = hidden.clone() if any(e.add_embedding for e in self.spec.schedule) else None
         delta = None
+        if self.spec.streams:
+            hidden = ops.hyper_expand(hidden, self.spec.streams)
         for pos, entry in enumerate(self.spec.schedule):
             if entry.add_embedding:
                 delta = ops.stream_add(hidden, start, delta)
             hidden, delta = self.blocks[entry.layer].forward(hidden, delta, ctx, cache_views[pos])
         if ctx.num_logit_rows == 0:
             return None
+        if self.spec.streams:
+            # the copies' sum, with the last sublayer's result written on the way
+            hidden, delta = ops.hyper_collapse(hidden, delta), None
         normed = Block.run_norm(self.final_norm, hidden, delta, ctx, rows=ctx.logit_rows)
         return self.head.forward(normed)

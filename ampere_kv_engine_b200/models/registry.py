@@ -41,13 +41,13 @@ def architecture_of(raw_config: dict) -> Architecture:
 
 def load_config(model_dir: str):
     """(architecture, typed config) of a model folder."""
-    from . import qwen3, renadra, sukalorn, zifuzen  # noqa: F401  (registers the built-in architectures)
+    from . import qwen3, renadra, sukalorn, zavizen, zifuzen  # noqa: F401  (registers the built-in architectures)
     raw = read_config_json(model_dir)
     arch = architecture_of(raw)
     return arch, arch.config_class.from_dict(raw)
 
 
 def config_from_dict(raw: dict):
-    from . import qwen3, renadra, sukalorn, zifuzen  # noqa: F401
+    from . import qwen3, renadra, sukalorn, zavizen, zifuzen  # noqa: F401
     arch = architecture_of(raw)
     return arch, arch.config_class.from_dict(raw)

@@ -6,8 +6,8 @@ computes on the flat token batch of one step.  Parts never look at a model confi
 and do not know which architecture uses them; the reference, by contrast, wires one model's
 attribute paths into every function (ampere_kv/runner.py:60-77, 102-179).
 
-Kinds are looked up in seven registries (mixers, feed-forwards, norms, position encodings,
-blocks, embeddings, heads).  Registering a new kind is one decorator call and needs no change
+Kinds are looked up in eight registries (mixers, feed-forwards, norms, position encodings,
+blocks, embeddings, heads, and the connections between a sublayer and a stream kept in several copies).  Registering a new kind is one decorator call and needs no change
 here.
 """
 
@@ -182,6 +182,21 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Connection(Part):
+    """How one sublayer reads from and writes to a residual stream that is kept in several copies per token
+    ([tokens, streams, width] float32)."""
+
+    def read(self, streams: torch.Tensor, pending, ctx) -> torch.Tensor:
+        """Apply ``pending`` (what the sublayer before left unwritten, or None) to ``streams`` in place and return this
+        sublayer's normed input [tokens, width] in the compute dtype."""
+        raise NotImplementedError
+
+    def write(self, y: torch.Tensor):
+        """What to hand to the next ``read`` (or to the model's end) so that the sublayer's result ``y`` gets
+        written back."""
+        raise NotImplementedError
+
+
 class Embedding(Part):
     """Token ids to the float32 residual stream."""
 
@@ -307,6 +322,7 @@ POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
+CONNECTIONS = Registry("connection")
 Block.ROLE_REGISTRIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "mixer_norm": NORMS,
                          "feed_forward_norm": NORMS}
 
@@ -317,6 +333,7 @@ register_position_encoding = POSITION_ENCODINGS.register
 register_block = BLOCKS.register
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
+register_connection = CONNECTIONS.register
 
 
 def build_part(registry: Registry, spec: PartSpec, *, hidden_size: int, dtype: torch.dtype,

@@ -12,6 +12,11 @@
     q, k, v = silu(W_q x), silu(W_k x), silu(W_v x);   a = decay[head] for every row
     y = W_o ( concat_h(o_h) / sqrt(mean over all heads of o^2 + eps) * norm * sigmoid(W_g x) )     norm: [heads * v_dim]
 
+``retention``: a constant decay per head, queries and keys turned by position, no activation.
+
+    q, k = rope(W_q x), rope(W_k x) * head_dim^-1/2;   v = W_v x;   a = decay[head] for every row
+    y = W_o ( concat_h( o_h / sqrt(mean(o_h^2) + eps) ) * silu(W_g x) )          no norm weight
+
 One product makes all projections of a token; ``ops.linear_scan`` applies the activations and gates in float32 and
 walks the step's tokens of every sequence in order, from and into the request's state slot (so the memory after a
 token is the same however the tokens were cut into steps); ``ops.group_norm_gate`` norms what was read out.  A
@@ -23,7 +28,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import CacheSpec, Mixer, ParamSpec, register_mixer
+from .base import POSITION_ENCODINGS, CacheSpec, Mixer, ParamSpec, build_part, register_mixer
 
 
 class _LinearMemory(Mixer):
@@ -139,3 +144,66 @@ class LightningAttention(_LinearMemory):
                             k_off=self.qk_width, v_off=2 * self.qk_width, decay=self.decay)
         return ops.group_norm_gate(o, self.norm_weight, group=self.v_width, eps=self.norm_eps, out_dtype=x.dtype,
                                    factor=self.out_scale, x=x, gate_off=2 * self.qk_width + self.v_width)
+
+
+@register_mixer("retention")
+class Retention(_LinearMemory):
+    """params: ``num_heads``, ``head_dim``, ``v_dim``, ``decay`` (a number per head), ``position_encoding`` (a
+    PartSpec of a rope in the half layout), ``key_scale`` (None: ``head_dim ** -0.5``, applied after the turn),
+    ``norm_eps``, ``names`` (local tensor names of q, k, v, gate, out).  Each head's read-out is divided by its root
+    mean square (no weight) and multiplied by ``silu`` of the gate projection."""
+
+    NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "gate": "g_proj.weight",
+             "out": "o_proj.weight"}
+
+    def __init__(self, spec, **kw):
+        super().__init__(spec, **kw)
+        self._sizes(spec.params, "retention")
+        decay = [float(d) for d in spec.params["decay"]]
+        if len(decay) != self.num_heads:
+            raise ValueError(f"retention: {len(decay)} decay rates for {self.num_heads} heads")
+        self.decay = torch.tensor(decay, dtype=torch.float64).to(torch.float32).to(self.device)
+        key_scale = spec.params.get("key_scale")
+        self.key_scale = float(key_scale) if key_scale is not None else self.head_dim ** -0.5
+        self.names = dict(self.NAMES, **(spec.params.get("names") or {}))
+        self.position_encoding = build_part(POSITION_ENCODINGS, spec.params["position_encoding"],
+                                            hidden_size=self.hidden_size, dtype=self.dtype, device=self.device)
+        table = getattr(self.position_encoding, "rotary_table", None)
+        if table is None:
+            raise ValueError("retention: the position encoding has no rotary table")
+        self.freq, self.rotary_dims, layout, factor = table()
+        if layout != "half" or factor != 1.0 or self.rotary_dims > self.head_dim:
+            raise ValueError("retention: queries and keys are turned in the half layout, without a factor, over at "
+                             "most the head's width")
+        self.w_in = self.w_o = None
+
+    def children(self):
+        return (self.position_encoding,)
+
+    def param_specs(self):
+        h, n = self.hidden_size, self.names
+        return {
+            n["q"]: ParamSpec((self.qk_width, h)),
+            n["k"]: ParamSpec((self.qk_width, h)),
+            n["v"]: ParamSpec((self.v_width, h)),
+            n["gate"]: ParamSpec((self.v_width, h)),
+            n["out"]: ParamSpec((h, self.v_width)),
+        }
+
+    def load(self, tensors):
+        n = self.names
+        self.w_in = torch.cat([tensors[n[k]] for k in ("q", "k", "v", "gate")], dim=0).contiguous()   # [q | k | v | g]
+        self.w_o = tensors[n["out"]].contiguous()
+
+    def heads_forward(self, x, ctx, cache):
+        if cache.state is None:
+            raise ValueError("retention: the cache manager gave this position no state")
+        x = ops.linear(x, self.w_in, status=ctx.status)
+        rows = ops.rotary_rows(x, ctx.positions, self.freq, num_heads=self.num_heads, head_dim=self.head_dim,
+                               v_dim=self.v_dim, rotary_dims=self.rotary_dims, q_off=0, k_off=self.qk_width,
+                               v_off=2 * self.qk_width, k_scale=self.key_scale)
+        o = ops.linear_scan(rows, cache.state, ctx.cu_q, ctx.state_slots, num_heads=self.num_heads,
+                            head_dim=self.head_dim, v_dim=self.v_dim, mode="plain_decay", q_off=0,
+                            k_off=self.qk_width, v_off=2 * self.qk_width, decay=self.decay)
+        return ops.group_norm_gate(o, None, group=self.v_dim, eps=self.norm_eps, out_dtype=x.dtype,
+                                   factor=self.out_scale, x=x, gate_off=2 * self.qk_width + self.v_width, gate="silu")

@@ -8,6 +8,10 @@ projection, with an ``out_scale`` applied in float32 before the one rounding) an
 bias, the two output projections run as one product over the sides' outputs laid next to each other; otherwise each
 side runs whole and ``ops.scaled_sum`` adds them up (sides with a bias on their output projection, or kinds that do
 not offer the two methods).
+
+With ``out_norm`` each side's output is first RMS-normed over the model width with a learned weight of its own:
+``left_scale * norm_l(left(x)) + right_scale * norm_r(right(x))``.  The sides' output products then leave float32
+(the accumulators as they are), and one kernel norms both and adds them up (``ops.normed_pair_sum``).
 """
 
 from __future__ import annotations
@@ -18,12 +22,13 @@ import torch
 
 from ..config.spec import PartSpec
 from ..kernels import ops
-from .base import MIXERS, CacheSpec, Mixer, build_part, register_mixer
+from .base import MIXERS, CacheSpec, Mixer, ParamSpec, build_part, register_mixer
 
 
 @register_mixer("parallel")
 class ParallelMixers(Mixer):
-    """params: ``left`` and ``right`` (PartSpecs of registered mixer kinds), ``left_scale``, ``right_scale``."""
+    """params: ``left`` and ``right`` (PartSpecs of registered mixer kinds), ``left_scale``, ``right_scale``,
+    ``out_norm`` (None, or ``{"eps", "left", "right"}``: the epsilon and the local names of the two norm weights)."""
 
     adds_residual = True
 
@@ -31,6 +36,8 @@ class ParallelMixers(Mixer):
         super().__init__(spec, **kw)
         p = spec.params
         self.scales = (float(p.get("left_scale", 1.0)), float(p.get("right_scale", 1.0)))
+        self.out_norm = dict(p["out_norm"]) if p.get("out_norm") else None
+        self.norm_weights = None
         sides = []
         for side, scale in zip((p["left"], p["right"]), self.scales):
             if not isinstance(side, PartSpec):
@@ -39,8 +46,8 @@ class ParallelMixers(Mixer):
         built = [build_part(MIXERS, side, hidden_size=self.hidden_size, dtype=self.dtype, device=self.device)
                  for side in sides]
         # one product for both output projections, if both sides can hand over what stands before theirs
-        self.joined = all(hasattr(m, "heads_forward") and hasattr(m, "out_projection")
-                          and not getattr(m, "out_bias", False) for m in built)
+        self.joined = self.out_norm is None and all(hasattr(m, "heads_forward") and hasattr(m, "out_projection")
+                                                    and not getattr(m, "out_bias", False) for m in built)
         if self.joined:
             built = [build_part(MIXERS, PartSpec(side.kind, dict(side.params, out_scale=scale), side.prefix),
                                 hidden_size=self.hidden_size, dtype=self.dtype, device=self.device)
@@ -74,9 +81,25 @@ class ParallelMixers(Mixer):
     def cache_spec(self) -> CacheSpec:
         return self._cache_spec
 
+    def param_specs(self):
+        if self.out_norm is None:
+            return {}
+        return {self.out_norm[side]: ParamSpec((self.hidden_size,), kind="vector", init="norm")
+                for side in ("left", "right")}
+
     def load(self, tensors):
         """The sides have their tensors by now (children load first is not promised, so the joined matrix is made at
         the first step)."""
+        if self.out_norm is not None:
+            self.norm_weights = tuple(tensors[self.out_norm[side]].float().contiguous() for side in ("left", "right"))
+
+    @staticmethod
+    def _float_output(side, x, ctx, cache):
+        """A side's output in float32: its last product's accumulators where the side lets us run that product."""
+        if hasattr(side, "heads_forward") and hasattr(side, "out_projection") and side.out_projection()[1] is None:
+            heads = side.heads_forward(x, ctx, cache)
+            return ops.linear(heads, side.out_projection()[0], out_dtype=torch.float32, status=ctx.status)
+        return side.forward(x, ctx, cache).float()
 
     def _views(self, cache):
         views, at = [], 0
@@ -91,6 +114,10 @@ class ParallelMixers(Mixer):
     def forward(self, x, ctx, cache, residual=None):
         left, right = self.sides
         cl, cr = self._views(cache)
+        if self.out_norm is not None:
+            return ops.normed_pair_sum(self._float_output(left, x, ctx, cl), self._float_output(right, x, ctx, cr),
+                                       *self.norm_weights, eps=float(self.out_norm["eps"]), sa=self.scales[0],
+                                       sb=self.scales[1], out_dtype=torch.float32)
         if self.joined:
             if self.w_o is None:
                 self.w_o = torch.cat((left.out_projection()[0], right.out_projection()[0]), dim=1).contiguous()

@@ -26,8 +26,8 @@ from .base import PositionEncoding, register_position_encoding
 @register_position_encoding("rope")
 class RotaryEmbedding(PositionEncoding):
     """params: ``theta``, ``rotary_dim``, ``layout`` (``"half"``, the default: dim i pairs with i + rotary_dim / 2;
-    ``"pairs"``: dim 2i with 2i + 1), ``scaling`` (None, or ``factor``, ``original``, ``fast``, ``slow`` of the
-    rescaling by wavelength)."""
+    ``"pairs"``: dim 2i with 2i + 1), ``scaling`` (None; ``factor`` alone: every frequency divided by it; or
+    ``factor``, ``original``, ``fast``, ``slow`` of the rescaling by wavelength)."""
 
     graph_safe = True
 
@@ -43,7 +43,14 @@ class RotaryEmbedding(PositionEncoding):
             raise ValueError(f"rope: layout must be 'half' or 'pairs', got {self.layout!r}")
         scaling = spec.params.get("scaling")
         self.factor = 1.0
-        if scaling is None and self.layout == "half":
+        if scaling is not None and "original" not in scaling:
+            # linear scaling: every frequency divided by one factor (positions stretched); float64, rounded once
+            stretch = float(scaling["factor"])
+            if stretch <= 0:
+                raise ValueError("rope: linear scaling needs a positive factor")
+            j = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
+            self.inv_freq = (self.theta ** (-2.0 * j / self.rotary_dim) / stretch).to(torch.float32).to(self.device)
+        elif scaling is None and self.layout == "half":
             exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.int64).float() / self.rotary_dim
             self.inv_freq = (1.0 / (self.theta ** exponent)).to(self.device)
         elif scaling is None:

@@ -2,6 +2,7 @@
 options that come with it:
 
     q, k (, v) = (W_q | W_k (| W_v)) x + biases          one product; biases on q, k, v and the output are optional
+    q, k      <- q / sqrt(mean(q^2) + eps) * w_q over ALL of q's heads at once, k likewise (``row_norm``), then
     q, k      <- the first rotary dims of every head turned by the token's position (``position_encoding``: a rope in
                  the half or the neighbouring-pairs layout, possibly with rescaled frequencies and a factor)
     v          = the key head before its turn (``value_from_key``; there is no W_v), or the v head, optionally divided
@@ -34,14 +35,15 @@ class RotaryAttention(Mixer):
     ``position_encoding`` (a PartSpec of a rope), ``bias`` (a tuple of the projections that carry one, of ``q``, ``k``,
     ``v``, ``out``), ``value_from_key``, ``value_norm`` and ``norm_eps``, ``softcap``, ``window``, ``keep_first``,
     ``weights`` (``"softmax"`` or ``"sigmoid"``), ``head_bias`` (bool: a learned number per head added to the score
-    inside the sigmoid), ``out_scale``, ``names`` (local tensor names of q, k, v, out, head_bias; a bias is the
-    matrix's name with ``bias_suffix`` added)."""
+    inside the sigmoid), ``out_scale``, ``row_norm`` (bool: a weighted RMS norm over the whole q projection and over
+    the whole k projection before the turn, ``norm_eps`` inside the root), ``names`` (local tensor names of q, k, v,
+    out, head_bias, q_norm, k_norm; a bias is the matrix's name with ``bias_suffix`` added)."""
 
     graph_safe = True
     adds_residual = True
 
     NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "out": "o_proj.weight",
-             "head_bias": "head_bias"}
+             "head_bias": "head_bias", "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
 
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)
@@ -76,6 +78,8 @@ class RotaryAttention(Mixer):
         if self.has_head_bias and self.weights != "sigmoid":
             raise ValueError("rotary_attention: a bias per head only matters inside the sigmoid")
         self.out_scale = float(p.get("out_scale", 1.0))
+        self.row_norm = bool(p.get("row_norm", False))
+        self.q_norm = self.k_norm = None
         self.names = dict(self.NAMES, **(p.get("names") or {}))
         self.bias_suffix = str(p.get("bias_suffix", ".bias"))
         self.position_encoding = build_part(POSITION_ENCODINGS, p["position_encoding"], hidden_size=self.hidden_size,
@@ -121,6 +125,9 @@ class RotaryAttention(Mixer):
                 specs[n[key] + self.bias_suffix] = ParamSpec((rows,), kind="bias")
         if self.has_head_bias:
             specs[n["head_bias"]] = ParamSpec((self.num_heads,), kind="vector", init="around_zero")
+        if self.row_norm:
+            specs[n["q_norm"]] = ParamSpec((self.num_heads * self.head_dim,), kind="vector", init="norm")
+            specs[n["k_norm"]] = ParamSpec((self.num_kv_heads * self.head_dim,), kind="vector", init="norm")
         specs[n["out"]] = ParamSpec((h, self.num_heads * self.v_dim))
         if "out" in self.bias:
             specs[n["out"] + self.bias_suffix] = ParamSpec((h,), kind="bias")
@@ -138,6 +145,9 @@ class RotaryAttention(Mixer):
             self.b_o = tensors[n["out"] + self.bias_suffix].contiguous()
         if self.has_head_bias:
             self.head_bias = tensors[n["head_bias"]].float().contiguous()
+        if self.row_norm:
+            self.q_norm = tensors[n["q_norm"]].float().contiguous()
+            self.k_norm = tensors[n["k_norm"]].float().contiguous()
 
     def heads_forward(self, x, ctx, cache) -> torch.Tensor:
         """Everything before the output projection: [tokens, heads * v_dim], each head's output times ``out_scale``."""
@@ -150,7 +160,7 @@ class RotaryAttention(Mixer):
                             num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
                             v_dim=self.v_dim, rotary_dims=self.rotary_dims, layout=self.layout, factor=self.factor,
                             value_from_key=self.value_from_key, value_norm=self.value_norm, eps=self.norm_eps,
-                            status=ctx.status)
+                            status=ctx.status, q_norm=self.q_norm, k_norm=self.k_norm, row_norm_eps=self.norm_eps)
         out = torch.empty((q.shape[0], self.num_heads * self.v_dim), dtype=q.dtype, device=q.device)
         run_attention(ctx, group, q, k_cache, v_cache, out, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
                       v_dim=self.v_dim, scale=self.scale, window=self.window, softcap=self.softcap,

@@ -1,13 +1,14 @@
 """A feed-forward of many small gated experts of which every token uses a few, plus an optional shared expert.
 
     z       = W_r x                         router logits, float32
-    s       = sigmoid(z)                    scores
+    s       = sigmoid(z)                    scores (``score="softmax"``: softmax of z over all experts)
     c       = s + correction                choice scores (the weights below use s)
     groups  : the experts form ``groups`` equal runs of neighbours; a group's score is the sum of its ``group_top``
               largest c; only experts of the ``keep_groups`` best groups can be chosen
     chosen  = the ``top`` allowed experts with the largest c
     w_e     = s_e / (sum of the chosen s + weight_eps) * route_scale
     expert  : g = min(W_gate x, limit); u = clamp(W_up x, -limit, limit); W_down (g * sigmoid(slope * g) * (u + 1))
+              (``activation="silu"``: plain W_down (silu(W_gate x) * W_up x), no clamp)
     y       = sum_e w_e expert_e(x)  +  shared(x)
 
 Everything runs on the device from the batch layout alone (no host read of the routing), so a decode step through it
@@ -28,9 +29,10 @@ from .base import FeedForward, ParamSpec, register_feed_forward
 @register_feed_forward("routed_experts")
 class RoutedExperts(FeedForward):
     """params: ``experts``, ``top``, ``groups`` and ``keep_groups`` (default 1 / 1: no groups), ``group_top``
-    (default 2), ``route_scale``, ``weight_eps``, ``score`` (only ``"sigmoid"``), ``correction`` (bool, default True:
-    a learned per-expert offset of the choice scores), ``intermediate_size`` and ``limit`` of an expert,
-    ``swish_slope``, ``shared`` (None, or ``{"intermediate_size", "limit"}``), ``names`` (``expert`` with ``{}`` for
+    (default 2; 1: a group is scored by its best expert), ``route_scale``, ``weight_eps``, ``score`` (``"sigmoid"`` or
+    ``"softmax"``), ``correction`` (bool, default True: a learned per-expert offset of the choice scores),
+    ``activation`` (``"clamped_swish"``, the default, with ``limit`` and ``swish_slope``; or ``"silu"``),
+    ``intermediate_size`` of an expert, ``shared`` (None, or ``{"intermediate_size", "limit"}``), ``names`` (``expert`` with ``{}`` for
     the index, ``gate``, ``up``, ``down``, ``router``, ``correction``, ``shared``)."""
 
     graph_safe = True
@@ -54,16 +56,24 @@ class RoutedExperts(FeedForward):
         if self.experts > ops.MOE_MAX_EXPERTS or self.top > ops.MOE_MAX_TOP:
             raise ValueError(f"routed_experts: the kernels take up to {ops.MOE_MAX_EXPERTS} experts and a top of "
                              f"{ops.MOE_MAX_TOP}")
-        if p.get("score", "sigmoid") != "sigmoid":
-            raise ValueError("routed_experts: only sigmoid scores are built")
+        self.score = str(p.get("score", "sigmoid"))
+        if self.score not in ops.MOE_SCORES:
+            raise ValueError(f"routed_experts: score must be one of {sorted(ops.MOE_SCORES)}, got {self.score!r}")
+        self.activation = str(p.get("activation", "clamped_swish"))
+        if self.activation not in ("clamped_swish", "silu"):
+            raise ValueError(f"routed_experts: activation must be 'clamped_swish' or 'silu', got {self.activation!r}")
         self.route_scale = float(p.get("route_scale", 1.0))
         self.weight_eps = float(p.get("weight_eps", 1e-20))
         self.has_correction = bool(p.get("correction", True))
-        self.intermediate_size, self.limit = int(p["intermediate_size"]), float(p["limit"])
-        self.swish_slope = float(p.get("swish_slope", 1.702))
+        self.intermediate_size = int(p["intermediate_size"])
         shared = p.get("shared")
         self.shared_size = int(shared["intermediate_size"]) if shared else 0
-        self.shared_limit = float(shared["limit"]) if shared else 0.0
+        if self.activation == "silu":
+            # the clamped form with nothing to clamp, a slope of one and no offset on the up half is SiLU times up
+            self.limit, self.swish_slope, self.up_offset, self.shared_limit = float("inf"), 1.0, 0.0, float("inf")
+        else:
+            self.limit, self.swish_slope, self.up_offset = float(p["limit"]), float(p.get("swish_slope", 1.702)), 1.0
+            self.shared_limit = float(shared["limit"]) if shared else 0.0
         self.names = dict(self.NAMES, **(p.get("names") or {}))
         self.w_router = self.correction = self.w_gate_up = self.w_down = self.shared_gate_up = self.shared_down = None
 
@@ -104,15 +114,19 @@ class RoutedExperts(FeedForward):
         logits = ops.moe_router_logits(x, self.w_router, status=status)
         chosen, weights = ops.moe_route(logits, self.correction, top=self.top, groups=self.groups,
                                         keep_groups=self.keep_groups, group_top=self.group_top,
-                                        scale=self.route_scale, weight_eps=self.weight_eps)
+                                        scale=self.route_scale, weight_eps=self.weight_eps, score=self.score)
         order, offsets = ops.moe_sort(chosen, self.experts)
         act = ops.moe_gate_up(x, self.w_gate_up, order, offsets, top=self.top, limit=self.limit,
-                              slope=self.swish_slope)
+                              slope=self.swish_slope, up_offset=self.up_offset)
         parts = ops.moe_down(act, self.w_down, order, offsets, weights)
         shared = None
         if self.shared_size:
-            both = ops.linear(x, self.shared_gate_up, status=status)
-            shared = ops.linear(ops.glu(both, "clamped_swish", 0, self.shared_limit, self.swish_slope),
-                                self.shared_down, status=status)
+            if self.activation == "silu":
+                shared = ops.linear(ops.gated_linear(x, self.shared_gate_up, 0, status=status), self.shared_down,
+                                    status=status)
+            else:
+                both = ops.linear(x, self.shared_gate_up, status=status)
+                shared = ops.linear(ops.glu(both, "clamped_swish", 0, self.shared_limit, self.swish_slope),
+                                    self.shared_down, status=status)
         result = ops.ExpertParts(parts, shared, self.top)
         return result if defer_sum else result.materialize()
