@@ -30,8 +30,9 @@ SIDE_SCALE = 0.5            # a parallel layer's result is half the sum of its n
 
 
 def _rope(rot: dict) -> PartSpec:
+    # a factor of one where the configuration names none: the frequencies are then formed in float64 and rounded once
     return PartSpec("rope", {"theta": rot["base"], "rotary_dim": rot["dims"], "layout": "half",
-                             "scaling": rot.get("scaling")}, "")
+                             "scaling": rot.get("scaling") or {"factor": 1.0}}, "")
 
 
 def _connection(config: ZavizenConfig, prefix: str, which: int) -> PartSpec:

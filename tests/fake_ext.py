@@ -372,11 +372,17 @@ class FakeExt:
     # ------------------------------------------------------------------ rotary positions, linear memories, the stream
 
     def rotary_prep(self, x, positions, slots, freq, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim, v_dim,
-                    rotary_dims, layout, factor=1.0, value_from_key=False, value_norm=False, eps=0.0, status=None):
+                    rotary_dims, layout, factor=1.0, value_from_key=False, value_norm=False, eps=0.0, status=None,
+                    q_norm=None, k_norm=None, row_norm_eps=0.0):
         n = x.shape[0]
         xf = x.float()
         a, b = num_heads * head_dim, num_kv_heads * head_dim
-        q, k = xf[:, :a].view(n, num_heads, head_dim), xf[:, a:a + b].view(n, num_kv_heads, head_dim)
+        q_row, k_row = xf[:, :a], xf[:, a:a + b]
+        k_plain = k_row.view(n, num_kv_heads, head_dim)
+        if q_norm is not None:
+            q_row = q_row * torch.rsqrt(q_row.square().mean(-1, keepdim=True) + row_norm_eps) * q_norm
+            k_row = k_row * torch.rsqrt(k_row.square().mean(-1, keepdim=True) + row_norm_eps) * k_norm
+        q, k = q_row.view(n, num_heads, head_dim), k_row.view(n, num_kv_heads, head_dim)
         angle = positions.float()[:, None] * freq.float()[None, :]
         cos, sin = (torch.cos(angle) * factor)[:, None, :], (torch.sin(angle) * factor)[:, None, :]
 
@@ -396,7 +402,7 @@ class FakeExt:
         if k_cache is None or slots is None:
             return
         if value_from_key:
-            v = k
+            v = k_plain
         else:
             v = xf[:, a + b:].view(n, num_kv_heads, v_dim)
             if value_norm:
@@ -412,11 +418,26 @@ class FakeExt:
         return ops.linear_scan_state_floats(heads, dim, v_dim)
 
     def linear_scan(self, x, state, cu_q, state_slots, out, num_heads, head_dim, v_dim, mode, q_off, k_off, v_off,
-                    gate_bias=None, lower=None, decay=None):
+                    gate_bias=None, lower=None, decay=None, qk_group=1, decay_off=0):
         H, D, V = num_heads, head_dim, v_dim
         cu, slots = cu_q.tolist(), state_slots.tolist()
         xf = x.float()
         silu = torch.nn.functional.silu
+        if mode >= 2:           # prepared float32 rows: no activation; a decay per head, or per head and token
+            for s, slot in enumerate(slots):
+                q0, q1 = cu[s], cu[s + 1]
+                if slot < 0 or q1 <= q0:
+                    continue
+                S = state[slot, :H * D * V].view(H, D, V).clone()
+                for t in range(q0, q1):
+                    q = xf[t, q_off:q_off + H // qk_group * D].view(-1, D).repeat_interleave(qk_group, 0)
+                    k = xf[t, k_off:k_off + H // qk_group * D].view(-1, D).repeat_interleave(qk_group, 0)
+                    v = xf[t, v_off:v_off + H * V].view(H, V)
+                    a = decay if mode == 2 else xf[t, decay_off:decay_off + H]
+                    S = a[:, None, None] * S + k[:, :, None] * v[:, None, :]
+                    out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1)
+                state[slot, :H * D * V] = S.reshape(-1)
+            return
         for s, slot in enumerate(slots):
             q0, q1 = cu[s], cu[s + 1]
             if slot < 0 or q1 <= q0:
@@ -435,14 +456,104 @@ class FakeExt:
                 out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1)
             state[slot, :H * D * V] = S.reshape(-1)
 
-    def group_norm_gate(self, o, out, weight, group, eps, factor=1.0, x=None, gate_off=0):
+    def group_norm_gate(self, o, out, weight, group, eps, factor=1.0, x=None, gate_off=0, gate_kind=0, gate_first=False,
+                        skip=None, skip_off=0, skip_coef=None, skip_head=1):
         n, width = o.shape
-        y = o.view(n, width // group, group)
-        y = y * torch.rsqrt(y.square().mean(-1, keepdim=True) + eps)
-        y = y.reshape(n, width) * weight.repeat(width // weight.numel()) * factor
+        y = o
+        gate = None
         if x is not None:
-            y = y * torch.sigmoid(x[:, gate_off:gate_off + width].float())
+            z = x[:, gate_off:gate_off + width].float()
+            gate = torch.sigmoid(z) if gate_kind == 0 else z * torch.sigmoid(z)
+        if skip is not None:
+            y = y + skip[:, skip_off:skip_off + width] * skip_coef.repeat_interleave(skip_head)
+        if gate is not None and gate_first:
+            y = y * gate
+        y = y.view(n, width // group, group)
+        y = (y * torch.rsqrt(y.square().mean(-1, keepdim=True) + eps)).reshape(n, width) * factor
+        if weight is not None:
+            y = y * weight.repeat(width // weight.numel())
+        if gate is not None and not gate_first:
+            y = y * gate
         out.copy_(y.to(out.dtype))
+
+    def rotary_rows(self, x, positions, freq, out, num_heads, head_dim, v_dim, rotary_dims, q_off, k_off, v_off,
+                    q_scale=1.0, k_scale=1.0):
+        n, H, D = x.shape[0], num_heads, head_dim
+        xf = x.float()
+        angle = positions.float()[:, None] * freq.float()[None, :]
+        cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+        half = rotary_dims // 2
+
+        def turn(t):
+            r = t.clone()
+            u, v = t[..., :half], t[..., half:rotary_dims]
+            r[..., :half] = u * cos - v * sin
+            r[..., half:rotary_dims] = v * cos + u * sin
+            return r
+
+        out[:, :H * D] = (turn(xf[:, q_off:q_off + H * D].view(n, H, D)) * q_scale).reshape(n, -1)
+        out[:, H * D:2 * H * D] = (turn(xf[:, k_off:k_off + H * D].view(n, H, D)) * k_scale).reshape(n, -1)
+        out[:, 2 * H * D:2 * H * D + H * v_dim] = xf[:, v_off:v_off + H * v_dim]
+
+    def ssm_prep(self, x, conv, conv_bias, step_bias, rate_log, state, tail_off, cu_q, state_slots, out, num_heads, v_dim,
+                 state_dim, groups, taps, conv_off, step_off):
+        H, P = num_heads, v_dim
+        inner, gn = H * P, groups * state_dim
+        channels = inner + 2 * gn
+        cu, slots = cu_q.tolist(), state_slots.tolist()
+        xf = x.float()
+        out.zero_()
+        for s, slot in enumerate(slots):
+            q0, q1 = cu[s], cu[s + 1]
+            if slot < 0 or q1 <= q0:
+                continue
+            before = state[slot, tail_off:tail_off + (taps - 1) * channels].view(taps - 1, channels)
+            stream = torch.cat((before, xf[q0:q1, conv_off:conv_off + channels]), dim=0)
+            y = torch.zeros(q1 - q0, channels) + (conv_bias if conv_bias is not None else 0.0)
+            for j in range(taps):
+                y = y + stream[j:j + q1 - q0] * conv[:, j]
+            y = y * torch.sigmoid(y)
+            dt = torch.nn.functional.softplus(xf[q0:q1, step_off:step_off + H] + step_bias)
+            out[q0:q1, :gn] = y[:, inner + gn:]
+            out[q0:q1, gn:2 * gn] = y[:, inner:inner + gn]
+            out[q0:q1, 2 * gn:2 * gn + inner] = y[:, :inner] * dt.repeat_interleave(P, 1)
+            out[q0:q1, 2 * gn + inner:2 * gn + inner + H] = torch.exp(-torch.exp(rate_log) * dt)
+            out[q0:q1, 2 * gn + inner + H:2 * gn + 2 * inner + H] = y[:, :inner]
+
+    def conv_tail(self, x, state, tail_off, cu_q, state_slots, conv_off, channels, taps):
+        cu, slots = cu_q.tolist(), state_slots.tolist()
+        for s, slot in enumerate(slots):
+            q0, q1 = cu[s], cu[s + 1]
+            if slot < 0 or q1 <= q0:
+                continue
+            before = state[slot, tail_off:tail_off + (taps - 1) * channels].view(taps - 1, channels)
+            stream = torch.cat((before, x[q0:q1, conv_off:conv_off + channels].float()), dim=0)
+            state[slot, tail_off:tail_off + (taps - 1) * channels] = stream[stream.shape[0] - (taps - 1):].reshape(-1)
+
+    @staticmethod
+    def _hyper_write(x, y, mix, write, scale):
+        z = y.float() if scale is None else y.float() * scale
+        return torch.einsum("st,nsw->ntw", mix, x) + write[None, :, None] * z[:, None, :]
+
+    def hyper_step(self, x, y, mix, write, scale, read, weight, eps, out, rows=None, status=None):
+        if y is not None:
+            x.copy_(self._hyper_write(x, y, mix, write, scale))
+        if out is not None:
+            u = torch.einsum("s,nsw->nw", read, x)
+            if rows is not None:
+                u = u[rows.long()]
+            out.copy_((u * torch.rsqrt(u.square().mean(-1, keepdim=True) + eps) * weight).to(out.dtype))
+
+    def hyper_collapse(self, x, y, mix, write, scale, total):
+        total.copy_((x if y is None else self._hyper_write(x, y, mix, write, scale)).sum(1))
+
+    def hyper_expand(self, hidden, x):
+        x.copy_(hidden[:, None, :].expand_as(x))
+
+    def normed_pair_sum(self, a, b, wa, wb, out, eps, sa, sb):
+        na = a * torch.rsqrt(a.square().mean(-1, keepdim=True) + eps) * wa
+        nb = b * torch.rsqrt(b.square().mean(-1, keepdim=True) + eps) * wb
+        out.copy_((sa * na + sb * nb).to(out.dtype))
 
     def pair_rows_add(self, hidden, ids, sampled, positions, cu_q, state_slots, last_token, table, vocab, buckets,
                       mul_prev, mul_cur):
@@ -471,10 +582,11 @@ class FakeExt:
 
     # ------------------------------------------------------------------ routed experts
 
-    def moe_route(self, logits, correction, chosen, weights, groups, keep_groups, group_top, scale, weight_eps):
+    def moe_route(self, logits, correction, chosen, weights, groups, keep_groups, group_top, scale, weight_eps,
+                  score_kind=0):
         n, E = logits.shape
         top = chosen.shape[1]
-        s = torch.sigmoid(logits.float())
+        s = torch.sigmoid(logits.float()) if score_kind == 0 else torch.softmax(logits.float(), dim=-1)
         c = s if correction is None else s + correction
         per = E // groups
         grouped = c.view(n, groups, per)
@@ -499,7 +611,7 @@ class FakeExt:
         offsets[0] = 0
         offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
 
-    def moe_gate_up(self, x, w_gate_up, order, offsets, act, top, limit, slope, form=0):
+    def moe_gate_up(self, x, w_gate_up, order, offsets, act, top, limit, slope, form=0, up_offset=1.0):
         inter = w_gate_up.shape[1] // 2
         off = offsets.tolist()
         for e in range(len(off) - 1):
@@ -508,7 +620,7 @@ class FakeExt:
                 continue
             both = x[rows // top].float() @ w_gate_up[e].float().T
             g, u = both[:, :inter].clamp(max=limit), both[:, inter:].clamp(min=-limit, max=limit)
-            act[off[e]:off[e + 1]] = (g * torch.sigmoid(slope * g) * (u + 1)).to(act.dtype)
+            act[off[e]:off[e + 1]] = (g * torch.sigmoid(slope * g) * (u + up_offset)).to(act.dtype)
 
     def moe_down(self, act, w_down, order, offsets, weights, out, form=0):
         off = offsets.tolist()

@@ -147,27 +147,37 @@ def gated_expert(h, w, prefix):
     return (silu(h @ w[f"{prefix}.gate"].T) * (h @ w[f"{prefix}.up"].T)) @ w[f"{prefix}.down"].T
 
 
-def route(logits, router):
-    """logits [T, experts] -> (chosen [T, top] long, weights [T, top])."""
+def route(logits, router, margins=None):
+    """logits [T, experts] -> (chosen [T, top] long, weights [T, top]).  ``margins`` (a list) receives, per token, by
+    how much (in logits) the last kept group and the last chosen expert lead the first ones left out."""
     E, top = int(router["experts"]), int(router["top"])
     s = torch.softmax(logits, dim=-1)
     allowed = torch.ones_like(s, dtype=torch.bool)
     groups = router.get("groups")
+    lead = torch.full((logits.shape[0],), float("inf"), dtype=logits.dtype)
     if groups is not None:
         count, keep = int(groups["count"]), int(groups["keep"])
         best = s.view(-1, count, E // count).max(dim=-1).values
         kept = best.topk(keep, dim=-1).indices
         mask = torch.zeros_like(best, dtype=torch.bool).scatter_(1, kept, True)
         allowed = mask[:, :, None].expand(-1, -1, E // count).reshape(-1, E)
+        if keep < count:
+            ranked = logits.view(-1, count, E // count).max(dim=-1).values.sort(dim=-1, descending=True).values
+            lead = torch.minimum(lead, ranked[:, keep - 1] - ranked[:, keep])
     chosen = s.masked_fill(~allowed, -1.0).topk(top, dim=-1).indices
+    if margins is not None:
+        ranked = logits.masked_fill(~allowed, float("-inf")).sort(dim=-1, descending=True).values
+        if top < int(allowed[0].sum()):
+            lead = torch.minimum(lead, ranked[:, top - 1] - ranked[:, top])
+        margins.append(lead)
     picked = s.gather(1, chosen)
     return chosen, picked / (picked.sum(-1, keepdim=True) + WEIGHT_EPS) * float(router["scale"])
 
 
-def feed_forward(h, w, prefix, mlp):
+def feed_forward(h, w, prefix, mlp, margins=None):
     if mlp.get("kind", "dense") == "dense":
         return gated_expert(h, w, prefix)
-    chosen, weights = route((h @ w[f"{prefix}.router"].T).float().to(h.dtype), mlp["router"])
+    chosen, weights = route(h @ w[f"{prefix}.router"].T, mlp["router"], margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, c in zip(chosen[t].tolist(), weights[t]):
@@ -193,7 +203,7 @@ def sublayer(xs, w, hc, scale_vector, norm_weight, eps, fn):
     return torch.einsum("sr,stw->rtw", w[f"{hc}.mix"], xs) + w[f"{hc}.out"][:, None, None] * y
 
 
-def forward_streams(w, raw, tokens, dtype=torch.float64):
+def forward_streams(w, raw, tokens, dtype=torch.float64, margins=None):
     """The sum of the streams after every layer run, [runs, T, width], and the final streams."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps = float(raw["norm"]["eps"])
@@ -209,12 +219,26 @@ def forward_streams(w, raw, tokens, dtype=torch.float64):
         xs = sublayer(xs, w, f"{p}.hc1", w[f"{p}.ls1"], w[f"{p}.norm1"], eps, mix)
         if layer.get("mlp") is not None:
             xs = sublayer(xs, w, f"{p}.hc2", w[f"{p}.ls2"], w[f"{p}.norm2"], eps,
-                          lambda h: feed_forward(h, w, f"{p}.mlp", layer["mlp"]))
+                          lambda h: feed_forward(h, w, f"{p}.mlp", layer["mlp"], margins))
         after.append(xs.sum(0))
     return torch.stack(after), xs
 
 
-def forward_logits(w, raw, tokens, dtype=torch.float64):
+def forward_logits(w, raw, tokens, dtype=torch.float64, margins=None):
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
-    _, xs = forward_streams(w, raw, tokens, dtype)
+    _, xs = forward_streams(w, raw, tokens, dtype, margins)
     return offset_norm(xs.sum(0), w["final.norm"], float(raw["norm"]["eps"])) @ w["head"].T
+
+
+def forward(raw, w, tokens, margins=None):
+    """Logits of every position, [T, vocab], in the dtype of the weights."""
+    return forward_logits(w, raw, tokens, dtype=w["embed"].dtype, margins=margins)
+
+
+def greedy_generate(raw, w, prompt, count):
+    ids, out = list(prompt), []
+    for _ in range(count):
+        token = int(forward(raw, w, ids)[-1].argmax())
+        out.append(token)
+        ids.append(token)
+    return out
