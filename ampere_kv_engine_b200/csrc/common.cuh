@@ -113,6 +113,50 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// Thread-block clusters for row-wise kernels on few rows: the CTAs of a cluster share one row and each takes a slice
+// of its columns; what they need of each other is a sum.  Outside a cluster launch the size is one.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t n;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n));
+  return n;
+}
+// Sum over all threads of all CTAs of the cluster; every thread gets the result, added up in rank order (the same
+// bits in every CTA).  `scratch` must hold 34 floats of shared memory.  Every CTA of the cluster must call it, the
+// same number of times; the second barrier keeps a CTA's shared memory alive until its peers have read it.
+__device__ __forceinline__ float cluster_sum(float v, float* scratch) {
+  v = block_sum(v, scratch);
+  const uint32_t n = cluster_size();
+  if (n == 1) return v;
+  if (threadIdx.x == 0) scratch[33] = v;
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+  const uint32_t local = (uint32_t)__cvta_generic_to_shared(scratch + 33);
+  float total = 0.f;
+  for (uint32_t r = 0; r < n; ++r) {
+    uint32_t remote;
+    float part;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(r));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part) : "r"(remote) : "memory");
+    total += part;
+  }
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+  return total;
+}
+// How many CTAs should share a row of `width` columns when there are `rows` rows: one where the rows alone fill the
+// GPU, up to eight (the portable cluster size) where they are few.
+inline int row_cluster(int64_t rows, int width, int min_columns = 256) {
+  if (rows >= 256) return 1;
+  int parts = 1;
+  while (parts < 8 && rows * parts < 128 && width / (parts * 2) >= min_columns) parts *= 2;
+  return parts;
+}
+
 // The one bounded wait of the package: poll an mbarrier (shared-memory address) for the given phase parity at most
 // `limit` times.  False when the phase did not complete; the caller then records kWaitTimeout, stops issuing work,
 // and leaves the kernel in order.  Every mbarrier wait of the TMA / tcgen05 kernels goes through this loop.

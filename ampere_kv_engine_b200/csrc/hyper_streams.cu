@@ -11,6 +11,8 @@
 // between the sum of squares and the output.  hyper_collapse gives sum_t x_t with a write still pending, which is
 // what a final norm reads.  hyper_expand makes the S copies from one row.  Everything is float32; y may be float32
 // or bfloat16, the normed output is in the serving dtype.
+#include <algorithm>
+
 #include "common.cuh"
 #include "launchers.h"
 
@@ -22,10 +24,55 @@ __device__ __forceinline__ float load_y(const void* y, int y_dtype, int64_t i) {
   return y_dtype == kBFloat16 ? __bfloat162float(((const __nv_bfloat16*)y)[i]) : ((const float*)y)[i];
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256) hyper_step_kernel(HyperStepParams p) {
-  extern __shared__ float hyper_smem[];
-  __shared__ float scratch[33];
+template <int VEC>
+__device__ __forceinline__ void load_vec(const float* p, float (&v)[VEC]) {
+  if constexpr (VEC == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+    v[0] = *p;
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void store_vec(float* p, const float (&v)[VEC]) {
+  if constexpr (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  else *p = v[0];
+}
+template <int VEC>
+__device__ __forceinline__ void store_vec(__nv_bfloat16* p, const float (&v)[VEC]) {
+  if constexpr (VEC == 4) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&a);
+    raw.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+  } else {
+    *p = __float2bfloat16_rn(v[0]);
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void load_y_vec(const void* y, int y_dtype, int64_t i, float (&v)[VEC]) {
+  if (y_dtype == kBFloat16) {
+    const __nv_bfloat16* p = (const __nv_bfloat16*)y + i;
+    if constexpr (VEC == 4) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(p);
+      v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xffff0000u);
+      v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xffff0000u);
+    } else {
+      v[0] = __bfloat162float(*p);
+    }
+  } else {
+    load_vec<VEC>((const float*)y + i, v);
+  }
+}
+
+// A block per (row, slice of the columns); the blocks of a row form a cluster (grid y) and add up their sums of
+// squares through distributed shared memory.  VEC columns per thread and access (4 where the width allows 16-byte
+// accesses).
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) hyper_step_kernel(HyperStepParams p, int chunk) {
+  extern __shared__ __align__(16) float hyper_smem[];
+  __shared__ float scratch[34];
   __shared__ float coef[kHyperMaxStreams * kHyperMaxStreams + 2 * kHyperMaxStreams];
   pdl_launch_dependents();
   const int S = p.streams, W = p.width;
@@ -40,48 +87,80 @@ __global__ void __launch_bounds__(256) hyper_step_kernel(HyperStepParams p) {
   pdl_wait();
   __syncthreads();
   int64_t token = blockIdx.x;
+  bool bad = false;
   if (p.rows != nullptr) {
     token = p.rows[blockIdx.x];
-    if (token < 0 || token >= p.num_tokens) {
+    if (token < 0 || token >= p.num_tokens) {            // every block of the row sees the same: they skip together
       if (threadIdx.x == 0) set_status(p.status, kBadRow);
-      return;
+      bad = true;
+      token = 0;
     }
   }
+  const int c0 = blockIdx.y * chunk, c1 = min(W, c0 + chunk);
   float* x = p.x + token * (int64_t)S * W;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    float old[kHyperMaxStreams];
+  for (int c = c0 + threadIdx.x * VEC; c < c1 && !bad; c += blockDim.x * VEC) {
+    float old[kHyperMaxStreams][VEC];
 #pragma unroll
-    for (int s = 0; s < kHyperMaxStreams; ++s) old[s] = s < S ? x[(int64_t)s * W + c] : 0.f;
-    float u = 0.f;
+    for (int s = 0; s < kHyperMaxStreams; ++s)
+      if (s < S) load_vec<VEC>(x + (int64_t)s * W + c, old[s]);
+    float u[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) u[e] = 0.f;
     if (p.y != nullptr) {
-      float y = load_y(p.y, p.y_dtype, token * W + c);
-      if (p.scale != nullptr) y *= p.scale[c];
+      float y[VEC];
+      load_y_vec<VEC>(p.y, p.y_dtype, token * W + c, y);
+      if (p.scale != nullptr) {
+        float sc[VEC];
+        load_vec<VEC>(p.scale + c, sc);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) y[e] *= sc[e];
+      }
 #pragma unroll
       for (int t = 0; t < kHyperMaxStreams; ++t) {
         if (t >= S) break;
-        float v = write[t] * y;
+        float v[VEC];
 #pragma unroll
-        for (int s = 0; s < kHyperMaxStreams; ++s)
-          if (s < S) v = fmaf(mix[s * S + t], old[s], v);
-        x[(int64_t)t * W + c] = v;
-        u = fmaf(read[t], v, u);
+        for (int e = 0; e < VEC; ++e) v[e] = write[t] * y[e];
+#pragma unroll
+        for (int s = 0; s < kHyperMaxStreams; ++s) {
+          if (s < S) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] = fmaf(mix[s * S + t], old[s][e], v[e]);
+          }
+        }
+        store_vec<VEC>(x + (int64_t)t * W + c, v);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) u[e] = fmaf(read[t], v[e], u[e]);
       }
     } else {
 #pragma unroll
-      for (int s = 0; s < kHyperMaxStreams; ++s)
-        if (s < S) u = fmaf(read[s], old[s], u);
+      for (int s = 0; s < kHyperMaxStreams; ++s) {
+        if (s < S) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) u[e] = fmaf(read[s], old[s][e], u[e]);
+        }
+      }
     }
     if (p.out != nullptr) {
-      hyper_smem[c] = u;
-      ss = fmaf(u, u, ss);
+      store_vec<VEC>(hyper_smem + (c - c0), u);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) ss = fmaf(u[e], u[e], ss);
     }
   }
   if (p.out == nullptr) return;
-  ss = block_sum(ss, scratch);
+  ss = cluster_sum(ss, scratch);
+  if (bad) return;
   const float inv = 1.f / sqrtf(ss / (float)W + p.eps);
   T* out = (T*)p.out + (int64_t)blockIdx.x * W;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) out[c] = from_float<T>(hyper_smem[c] * inv * p.weight[c]);
+  for (int c = c0 + threadIdx.x * VEC; c < c1; c += blockDim.x * VEC) {
+    float u[VEC], w[VEC];
+    load_vec<VEC>(hyper_smem + (c - c0), u);
+    load_vec<VEC>(p.weight + c, w);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) u[e] *= inv * w[e];
+    store_vec<VEC>(out + c, u);
+  }
 }
 
 // out[n, c] = sum_t x_t after the pending write (if any): sum_s (sum_t mix[s, t]) x_s + (sum_t write[t]) scale y
@@ -124,26 +203,29 @@ __global__ void __launch_bounds__(256) hyper_expand_kernel(const float* __restri
   }
 }
 
-// out = sa * a / sqrt(mean(a^2) + eps) * wa + sb * b / sqrt(mean(b^2) + eps) * wb, a row per block; a and b float32
+// out = sa * a / sqrt(mean(a^2) + eps) * wa + sb * b / sqrt(mean(b^2) + eps) * wb; a block per (row, slice of the
+// columns), the blocks of a row a cluster (grid y); a and b float32
 template <typename T>
 __global__ void __launch_bounds__(256) normed_pair_sum_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                                               const float* __restrict__ wa, const float* __restrict__ wb,
-                                                              T* __restrict__ out, int W, float eps, float sa, float sb) {
-  __shared__ float scratch[33];
+                                                              T* __restrict__ out, int W, int chunk, float eps, float sa,
+                                                              float sb) {
+  __shared__ float scratch[34];
   pdl_launch_dependents();
   pdl_wait();
   const int64_t token = blockIdx.x;
+  const int c0 = blockIdx.y * chunk, c1 = min(W, c0 + chunk);
   const float* ra = a + token * W;
   const float* rb = b + token * W;
   float ssa = 0.f, ssb = 0.f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+  for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
     ssa = fmaf(ra[c], ra[c], ssa);
     ssb = fmaf(rb[c], rb[c], ssb);
   }
-  ssa = block_sum(ssa, scratch);
-  ssb = block_sum(ssb, scratch);
+  ssa = cluster_sum(ssa, scratch);
+  ssb = cluster_sum(ssb, scratch);
   const float ia = sa / sqrtf(ssa / (float)W + eps), ib = sb / sqrtf(ssb / (float)W + eps);
-  for (int c = threadIdx.x; c < W; c += blockDim.x)
+  for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x)
     out[token * W + c] = from_float<T>(ra[c] * ia * wa[c] + rb[c] * ib * wb[c]);
 }
 
@@ -159,14 +241,25 @@ int launch_hyper_step(const HyperStepParams& p, cudaStream_t stream) {
       (p.y != nullptr && (p.mix == nullptr || p.write == nullptr)) ||
       (p.out != nullptr && (p.read == nullptr || p.weight == nullptr)))
     return (int)cudaErrorInvalidValue;
-  const size_t smem = p.out != nullptr ? (size_t)p.width * sizeof(float) : 0;
-  auto kernel = p.dtype == kBFloat16 ? hyper_step_kernel<__nv_bfloat16> : hyper_step_kernel<float>;
+  // 16-byte accesses where every row, slice and operand starts on a 16-byte boundary
+  auto aligned = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
+  const bool wide = p.width % 4 == 0 && aligned(p.x) && aligned(p.y) && aligned(p.scale) && aligned(p.weight) &&
+                    aligned(p.out);
+  const int vec = wide ? 4 : 1;
+  const int parts = row_cluster(blocks, p.width);
+  const int chunk = ((p.width / vec + parts - 1) / parts) * vec;
+  const size_t smem = p.out != nullptr ? (size_t)chunk * sizeof(float) : 0;
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  void (*kernel)(HyperStepParams, int) =
+      p.dtype == kBFloat16 ? (wide ? hyper_step_kernel<__nv_bfloat16, 4> : hyper_step_kernel<__nv_bfloat16, 1>)
+                           : (wide ? hyper_step_kernel<float, 4> : hyper_step_kernel<float, 1>);
   if (smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
   }
-  return (int)launch_chain(kernel, dim3((unsigned)blocks), dim3(threads_for(p.width)), smem, stream, dim3(1, 1, 1), p);
+  const int threads = std::min(256, std::max(32, (chunk / vec + 31) / 32 * 32));
+  return (int)launch_chain(kernel, dim3((unsigned)blocks, (unsigned)parts), dim3(threads), smem, stream,
+                           dim3(1, parts, 1), p, chunk);
 }
 
 int launch_hyper_collapse(const HyperStepParams& p, float* sum, cudaStream_t stream) {
@@ -189,11 +282,15 @@ int launch_normed_pair_sum(const float* a, const float* b, const float* wa, cons
                            int64_t num_tokens, int width, float eps, float sa, float sb, int dtype, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (width < 1 || num_tokens > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  const int parts = row_cluster(num_tokens, width);
+  const int chunk = (width + parts - 1) / parts;
+  const int threads = std::min(256, std::max(32, (chunk + 31) / 32 * 32));
+  const dim3 grid((unsigned)num_tokens, (unsigned)parts), cluster(1, parts, 1);
   if (dtype == kBFloat16)
-    return (int)launch_chain(normed_pair_sum_kernel<__nv_bfloat16>, dim3((unsigned)num_tokens), dim3(threads_for(width)),
-                             0, stream, dim3(1, 1, 1), a, b, wa, wb, (__nv_bfloat16*)out, width, eps, sa, sb);
-  return (int)launch_chain(normed_pair_sum_kernel<float>, dim3((unsigned)num_tokens), dim3(threads_for(width)), 0,
-                           stream, dim3(1, 1, 1), a, b, wa, wb, (float*)out, width, eps, sa, sb);
+    return (int)launch_chain(normed_pair_sum_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, cluster, a, b, wa, wb,
+                             (__nv_bfloat16*)out, width, chunk, eps, sa, sb);
+  return (int)launch_chain(normed_pair_sum_kernel<float>, grid, dim3(threads), 0, stream, cluster, a, b, wa, wb,
+                           (float*)out, width, chunk, eps, sa, sb);
 }
 
 }  // namespace akv

@@ -23,7 +23,7 @@ namespace akv {
 namespace {
 
 constexpr int kPrepWarps = 4;
-constexpr int kRowWarps = 8;     // of the form with norms over whole rows: a block per token
+constexpr int kRowWarps = 4;     // of the form with norms over whole rows: a block per token, or a cluster of them
 
 // One head: src (T) -> dst (U), the first `rot` dims turned; every entry first times inv * w[d] when w is given (a
 // norm over the whole row of heads, whose root mean square the caller worked out), and times `scale` at the end.
@@ -111,26 +111,29 @@ __global__ void __launch_bounds__(kPrepWarps * 32) rotary_prep_kernel(RotaryPrep
 // then its warps take the heads in turn.
 template <typename T>
 __global__ void __launch_bounds__(kRowWarps * 32) rotary_prep_rows_kernel(RotaryPrepParams p) {
-  __shared__ float scratch[33];
+  __shared__ float scratch[34];
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t token = blockIdx.x;
   const int qw = p.num_heads * p.head_dim, kw = p.num_kv_heads * p.head_dim;
   const T* row = (const T*)p.x + token * p.x_stride;
+  // the blocks of a token (grid y, one cluster) take every gridDim.y-th run of the row for the sums, then every
+  // gridDim.y-th group of heads
+  const int first = blockIdx.y * blockDim.x + threadIdx.x, stride = gridDim.y * blockDim.x;
   float sq = 0.f, sk = 0.f;
-  for (int c = threadIdx.x; c < qw; c += blockDim.x) {
+  for (int c = first; c < qw; c += stride) {
     const float v = to_float<T>(row[c]);
     sq = fmaf(v, v, sq);
   }
-  for (int c = threadIdx.x; c < kw; c += blockDim.x) {
+  for (int c = first; c < kw; c += stride) {
     const float v = to_float<T>(row[qw + c]);
     sk = fmaf(v, v, sk);
   }
-  sq = block_sum(sq, scratch);
-  sk = block_sum(sk, scratch);
+  sq = cluster_sum(sq, scratch);
+  sk = cluster_sum(sk, scratch);
   const float inv_q = 1.f / sqrtf(sq / (float)qw + p.row_norm_eps), inv_k = 1.f / sqrtf(sk / (float)kw + p.row_norm_eps);
-  for (int h = threadIdx.x >> 5; h < p.num_heads + p.num_kv_heads; h += kRowWarps)
+  for (int h = blockIdx.y * kRowWarps + (threadIdx.x >> 5); h < p.num_heads + p.num_kv_heads; h += gridDim.y * kRowWarps)
     prep_head<T>(p, token, h, lane, inv_q, inv_k);
 }
 
@@ -167,11 +170,13 @@ int launch_rotary_prep(const RotaryPrepParams& p, cudaStream_t stream) {
   if ((p.q_norm == nullptr) != (p.k_norm == nullptr)) return (int)cudaErrorInvalidValue;
   if (p.q_norm != nullptr) {
     if (p.num_tokens > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+    // few tokens: up to eight blocks (a cluster) share a token's heads
+    int parts = 1;
+    while (parts < 8 && p.num_tokens * parts < 128 && (p.num_heads + p.num_kv_heads) >= 2 * parts * kRowWarps) parts *= 2;
+    const dim3 grid((unsigned)p.num_tokens, (unsigned)parts), cluster(1, parts, 1);
     if (p.dtype == kBFloat16)
-      return (int)launch_chain(rotary_prep_rows_kernel<__nv_bfloat16>, dim3((unsigned)p.num_tokens), dim3(kRowWarps * 32),
-                               0, stream, dim3(1, 1, 1), p);
-    return (int)launch_chain(rotary_prep_rows_kernel<float>, dim3((unsigned)p.num_tokens), dim3(kRowWarps * 32), 0,
-                             stream, dim3(1, 1, 1), p);
+      return (int)launch_chain(rotary_prep_rows_kernel<__nv_bfloat16>, grid, dim3(kRowWarps * 32), 0, stream, cluster, p);
+    return (int)launch_chain(rotary_prep_rows_kernel<float>, grid, dim3(kRowWarps * 32), 0, stream, cluster, p);
   }
   const int64_t items = p.num_tokens * (p.num_heads + p.num_kv_heads);
   const int64_t blocks = (items + kPrepWarps - 1) / kPrepWarps;

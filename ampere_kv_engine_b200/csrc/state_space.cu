@@ -46,19 +46,20 @@ __global__ void __launch_bounds__(256) ssm_prep_kernel(SsmPrepParams p) {
   const int slot = p.state_slots[s];
   const int width = 2 * gn + 2 * inner + H;
   if (slot < 0 || slot >= p.num_slots) {
-    for (int c = threadIdx.x; c < width; c += blockDim.x) out[c] = 0.f;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) out[c] = 0.f;
     return;
   }
+  // the blocks of a token (grid y) take every gridDim.y-th run of the channels; each works out the steps it needs
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
     const float dt = softplus_f(to_float<T>(x[token * p.x_stride + p.step_off + h]) + p.step_bias[h]);
     dt_s[h] = dt;
-    out[2 * gn + inner + h] = expf(-expf(p.rate_log[h]) * dt);
+    if (blockIdx.y == 0) out[2 * gn + inner + h] = expf(-expf(p.rate_log[h]) * dt);
   }
   __syncthreads();
   const int64_t seq_first = p.cu_q[s];
   const int offset = (int)(token - seq_first);               // tokens of this sequence before this one in the step
   const float* before = p.state + (int64_t)slot * p.state_stride + p.tail_off;      // [taps - 1, channels]
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
     const float* w = p.conv + (int64_t)c * taps;
     float y = p.conv_bias != nullptr ? p.conv_bias[c] : 0.f;
     for (int j = 0; j < taps; ++j) {
@@ -114,10 +115,13 @@ int launch_ssm_prep(const SsmPrepParams& p, cudaStream_t stream) {
   if (p.num_heads < 1 || p.num_heads > kSsmMaxHeads || p.groups < 1 || p.num_heads % p.groups || p.taps < 1 ||
       p.taps > kConvMaxTaps || p.num_tokens > 0x7fffffffLL || p.num_seqs < 1)
     return (int)cudaErrorInvalidValue;
+  const int channels = p.num_heads * p.v_dim + 2 * p.groups * p.state_dim;
+  int across = 1;                       // few tokens: several blocks share a token's channels
+  while (across < 16 && p.num_tokens * across < 256 && channels >= 2 * across * 256) across *= 2;
+  const dim3 grid((unsigned)p.num_tokens, (unsigned)across);
   if (p.dtype == kBFloat16)
-    return (int)launch_chain(ssm_prep_kernel<__nv_bfloat16>, dim3((unsigned)p.num_tokens), dim3(256), 0, stream,
-                             dim3(1, 1, 1), p);
-  return (int)launch_chain(ssm_prep_kernel<float>, dim3((unsigned)p.num_tokens), dim3(256), 0, stream, dim3(1, 1, 1), p);
+    return (int)launch_chain(ssm_prep_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, dim3(1, 1, 1), p);
+  return (int)launch_chain(ssm_prep_kernel<float>, grid, dim3(256), 0, stream, dim3(1, 1, 1), p);
 }
 
 int launch_conv_tail(const ConvTailParams& p, cudaStream_t stream) {

@@ -1,6 +1,6 @@
 """Benchmark of the engine on one B200: decode tokens per second at the Qwen3-8B shape.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference] [--shape 8b|14b|32b|sukalorn|zifuzen|renadra]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference] [--shape 8b|14b|32b|sukalorn|zifuzen|renadra|zavizen]
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch through the engine's own step
 function (every kernel of the model and the token choice); ``value`` is batch / step time, timed with CUDA
@@ -12,6 +12,8 @@ cache) with the copy bandwidth.  Weights are random (seeded), token ids syntheti
 ``--shape zifuzen`` does for the Zifuzen design what ``--shape sukalorn`` does for Sukalorn.
 ``--shape renadra`` sets four Renadra layers beside Zifuzen layers of equal size with dense feed-forwards, and
 Renadra's kernels alone beside the like kernels of the other designs.
+``--shape zavizen`` sets four Zavizen layers beside Renadra layers of equal size, and Zavizen's kernels alone beside the
+like kernels of the other designs.
 ``--shape sukalorn`` prints a line of its own: prefill and decode of four Sukalorn layers at two sizes beside Qwen3
 layers of equal size, and the attention kernels alone.
 Between timed steps nothing is flushed: every step streams the whole model (16 GB at full depth) through
@@ -547,6 +549,26 @@ def renadra_config(z: dict, layers: int) -> dict:
                        for i in range(layers)]}
 
 
+# Zavizen at the same sizes: four layers (parallel, mamba2, parallel, mamba2) on four copies of the stream, all with
+# dense feed-forwards, beside Renadra's four layers of the same width, heads, head size and feed-forward width: the
+# package's other design with mixers side by side, a decaying memory per head and a looped schedule.
+ZAVIZEN_STREAMS = 4
+
+
+def zavizen_config(z: dict, layers: int) -> dict:
+    d, h = z["dim"], z["memory_heads"]
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5,
+            "rot": {"base": 1000000.0, "dims": d // 2, "scaling": {"factor": 4.0}}}
+    right = {"heads": h, "dim": d, "vdim": d, "rot": {"base": 1000000.0, "dims": d},
+             "decay": [1.0 - 2.0 ** -(2 + 8 * i / max(1, h - 1)) for i in range(h)]}
+    mamba = {"heads": h, "vdim": d, "state": d, "groups": 1, "conv": 4, "norm_groups": 1}
+    pattern = [("parallel", {"left": left, "right": right}), ("mamba2", mamba)]
+    return {"architecture": "Zavizen", "vocab": SUKALORN_VOCAB, "width": z["width"], "norm": {"eps": 1e-6},
+            "streams": ZAVIZEN_STREAMS,
+            "layers": [{"type": pattern[i % 2][0], "mixer": json.loads(json.dumps(pattern[i % 2][1])),
+                        "mlp": {"kind": "dense", "ff": z["ff"]}} for i in range(layers)]}
+
+
 def zifuzen_dense_like(z: dict, layers: int) -> dict:
     attention = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
                  "scale": z["dim"] ** -0.5}
@@ -922,7 +944,159 @@ def sukalorn_shape(args, design: str = "sukalorn") -> int:
                 out[f"{name}_{case}"]["splits"] = splits
         return out
 
+    def zavizen_kernels_alone(z: dict) -> dict:
+        """The kernels that came with the Zavizen design by themselves at this size, each beside the like kernel of
+        another design: the scan on prepared rows with a constant decay and with a decay per token beside the
+        lightning scan (Renadra), the state-space preparation beside the delta rule's, the stream's write + read + norm
+        beside the residual add + RMS norm, the rotation with norms over whole rows beside the plain rotation, the
+        float32 rows, the norm with a skip term and a gate before it beside the gated norm over all heads, two normed
+        outputs summed beside the scaled sum.  A 2,048-token prompt as one sequence, and single tokens of `batch`
+        sequences."""
+        out = {}
+        H, D, V, W = z["memory_heads"], z["dim"], z["dim"], z["width"]
+        heads, kvh, page = z["heads"], z["kv_heads"], args.page_size
+        g = torch.Generator(device=device).manual_seed(3)
+        dev = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+        fp32_peak = peaks.get("fp32_tflops") or FP32_FMA_TFLOPS
+        floats = ops.linear_scan_state_floats(H, D, V)
+        taps, S = 4, ZAVIZEN_STREAMS
+        channels = H * V + 2 * D
+        delta_memory, delta_floats = ops.delta_state_floats(H, kvh, D, V, taps)
+        state = torch.zeros((batch + 1, max(floats + (taps - 1) * channels + 4, delta_floats)), device=device)
+        decay = torch.tensor(zavizen_config(z, 2)["layers"][0]["mixer"]["right"]["decay"], device=device)
+
+        def record(key, fn, *, flops=0.0, moved=0.0):
+            for _ in range(3):
+                fn()
+            ms = timed(fn, 5, flush_l2=True)
+            entry = {"ms": round(ms, 4)}
+            if flops:
+                entry["tflops"] = round(flops / (ms / 1000) / 1e12, 3)
+                entry["frac_of_fp32_fma_peak"] = round(flops / (ms / 1000) / 1e12 / fp32_peak, 4)
+            if moved:
+                entry["gbs"] = round(moved / (ms / 1000) / 1e9, 1)
+                entry["frac_of_hbm"] = round(moved / (ms / 1000) / 1e9 / peaks["hbm_gbs"], 4)
+            out[key] = entry
+
+        for name, lens in (("prompt", [PREFILL_TOKENS]), ("decode", [1] * batch)):
+            tokens = sum(lens)
+            cu, slots = dev([0] + [sum(lens[:i + 1]) for i in range(len(lens))]), dev(list(range(len(lens))))
+            rand = lambda *shape: torch.randn(shape, device=device, generator=g)
+            scan_flops = 5.0 * tokens * H * D * V
+            # retention: float32 rows [q | k | v] made by rotary_rows, then the scan with a constant decay
+            x = rand(tokens, 2 * H * D + 2 * H * V).to(torch.bfloat16)
+            positions = dev([i for n in lens for i in range(PROMPT_LEN, PROMPT_LEN + n)])
+            freq = (1000000.0 ** (-torch.arange(0, D, 2, device=device).float() / D)).contiguous()
+            record(f"{name}_rotary_rows", lambda: ops.rotary_rows(x, positions, freq, num_heads=H, head_dim=D, v_dim=V,
+                                                                  rotary_dims=D, q_off=0, k_off=H * D, v_off=2 * H * D,
+                                                                  k_scale=D ** -0.5),
+                   moved=tokens * (2.0 + 4.0) * (2 * H * D + H * V))
+            rows = ops.rotary_rows(x, positions, freq, num_heads=H, head_dim=D, v_dim=V, rotary_dims=D, q_off=0,
+                                   k_off=H * D, v_off=2 * H * D, k_scale=D ** -0.5)
+            kw = dict(num_heads=H, head_dim=D, v_dim=V, q_off=0, k_off=H * D, v_off=2 * H * D)
+            record(f"{name}_retention_scan", lambda: ops.linear_scan(rows, state, cu, slots, mode="plain_decay",
+                                                                     decay=decay, **kw),
+                   flops=scan_flops, moved=2.0 * 4 * len(lens) * floats + 4.0 * tokens * (2 * H * D + 2 * H * V))
+            record(f"{name}_like_lightning_scan", lambda: ops.linear_scan(x, state, cu, slots, mode="constant_decay",
+                                                                          decay=decay, **kw),
+                   flops=scan_flops, moved=2.0 * 4 * len(lens) * floats + 2.0 * tokens * 3 * H * D + 4.0 * tokens * H * V)
+            o = ops.linear_scan(rows, state, cu, slots, mode="plain_decay", decay=decay, **kw)
+            record(f"{name}_norm_per_head_silu_gate", lambda: ops.group_norm_gate(
+                o, None, group=V, eps=1e-6, out_dtype=torch.bfloat16, x=x, gate_off=2 * H * D + H * V, gate="silu"),
+                moved=8.0 * tokens * H * V)
+            norm_wide = torch.ones((H * V,), device=device)
+            record(f"{name}_like_norm_all_heads_gated", lambda: ops.group_norm_gate(
+                o, norm_wide, group=H * V, eps=1e-6, out_dtype=torch.bfloat16, x=x, gate_off=2 * H * D + H * V),
+                moved=8.0 * tokens * H * V)
+            # the state-space mixer: preparation, the scan with a decay per token (all heads on one q and k), the norm
+            xin = rand(tokens, 2 * H * V + 2 * D + H).to(torch.bfloat16)
+            conv, bias = torch.rand((channels, taps), device=device, generator=g) - 0.3, torch.zeros((channels,), device=device)
+            step_bias, rate_log = torch.full((H,), -3.0, device=device), torch.zeros((H,), device=device)
+            state.zero_()
+            prep_kw = dict(tail_off=floats, num_heads=H, v_dim=V, state_dim=D, groups=1, taps=taps, conv_off=H * V,
+                           step_off=H * V + channels)
+            width = ops.ssm_prep_width(H, V, D, 1)
+            record(f"{name}_ssm_prep", lambda: ops.ssm_prep(xin, conv, bias, step_bias, rate_log, state, cu, slots, **prep_kw),
+                   moved=tokens * (2.0 * (channels + H) + 4.0 * width))
+            prepared = ops.ssm_prep(xin, conv, bias, step_bias, rate_log, state, cu, slots, **prep_kw)
+            record(f"{name}_ssm_scan", lambda: ops.linear_scan(
+                prepared, state, cu, slots, num_heads=H, head_dim=D, v_dim=V, mode="token_decay", q_off=0, k_off=D,
+                v_off=2 * D, qk_group=H, decay_off=2 * D + H * V),
+                flops=scan_flops, moved=2.0 * 4 * len(lens) * floats + 4.0 * tokens * (2 * D + 2 * H * V + H))
+            so = ops.linear_scan(prepared, state, cu, slots, num_heads=H, head_dim=D, v_dim=V, mode="token_decay",
+                                 q_off=0, k_off=D, v_off=2 * D, qk_group=H, decay_off=2 * D + H * V)
+            skip = torch.ones((H,), device=device)
+            record(f"{name}_ssm_norm_skip_gate_first", lambda: ops.group_norm_gate(
+                so, norm_wide, group=H * V, eps=1e-6, out_dtype=torch.bfloat16, x=xin, gate_off=0, gate="silu",
+                gate_first=True, skip=prepared, skip_off=2 * D + H * V + H, skip_coef=skip, skip_head=V),
+                moved=12.0 * tokens * H * V)
+            record(f"{name}_conv_tail", lambda: ops.conv_tail(xin, state, cu, slots, tail_off=floats, conv_off=H * V,
+                                                              channels=channels, taps=taps))
+            # the like kernel: the delta rule's preparation at the same heads and widths
+            dch = 2 * kvh * D + H * V
+            xd = rand(tokens, dch + H * V + 2 * H).to(torch.bfloat16)
+            dconv = torch.rand((dch, taps), device=device, generator=g) - 0.3
+            state.zero_()
+            record(f"{name}_like_delta_prep", lambda: ops.delta_prep(
+                xd, dconv, step_bias, rate_log, state, cu, slots, unit_eps=1e-6, num_heads=H, num_kv_heads=kvh,
+                head_dim=D, v_dim=V, taps=taps), moved=tokens * (2.0 * (dch + 2 * H) + 4.0 * (dch + 2 * H)))
+            state.zero_()
+            # the stream in copies: write + read + norm in one pass, beside the residual add + RMS norm
+            streams = rand(tokens, S, W)
+            y = rand(tokens, W).to(torch.bfloat16)
+            pending = ops.HyperPending(y, torch.eye(S, device=device), torch.ones((S,), device=device),
+                                       torch.ones((W,), device=device))
+            read, weight = torch.ones((S,), device=device), torch.ones((W,), device=device)
+            record(f"{name}_hyper_step", lambda: ops.hyper_step(streams, pending, read, weight, 1e-6, torch.bfloat16),
+                   moved=tokens * W * (8.0 * S + 4.0))
+            hidden = rand(tokens, W)
+            record(f"{name}_like_add_rmsnorm", lambda: ops.add_rmsnorm(hidden, y, weight, 1e-6, torch.bfloat16),
+                   moved=tokens * W * 12.0)
+            a, b = rand(tokens, W), rand(tokens, W)
+            record(f"{name}_normed_pair_sum", lambda: ops.normed_pair_sum(a, b, weight, weight, eps=1e-6, sa=0.5, sb=0.5,
+                                                                          out_dtype=torch.float32),
+                   moved=tokens * W * 12.0)
+            ab, bb = a.to(torch.bfloat16), b.to(torch.bfloat16)
+            record(f"{name}_like_scaled_sum", lambda: ops.scaled_sum(ab, bb, 0.5, 0.5), moved=tokens * W * 6.0)
+            # the rotation before attention, with and without norms over the whole q and k rows
+            bf = dict(dtype=torch.bfloat16, device=device)
+            k_pages = torch.zeros((tokens // page + 1, kvh, page, D), **bf)
+            v_pages = torch.zeros((tokens // page + 1, kvh, page, D), **bf)
+            xp = rand(tokens, (heads + 2 * kvh) * D).to(torch.bfloat16)
+            slot_map = dev(list(range(tokens)))
+            half = freq[: D // 4].contiguous()
+            qn, kn = torch.ones((heads * D,), device=device), torch.ones((kvh * D,), device=device)
+            prep = dict(num_heads=heads, num_kv_heads=kvh, head_dim=D, v_dim=D, rotary_dims=D // 2, layout="half")
+            moved = 2.0 * tokens * ((heads + 2 * kvh) * D + heads * D + 2 * kvh * D)
+            record(f"{name}_rotary_prep_row_norms", lambda: ops.rotary_prep(
+                xp, positions, slot_map, half, k_pages, v_pages, q_norm=qn, k_norm=kn, row_norm_eps=1e-6, **prep), moved=moved)
+            record(f"{name}_like_rotary_prep", lambda: ops.rotary_prep(xp, positions, slot_map, half, k_pages, v_pages, **prep),
+                   moved=moved)
+        return out
+
     sizes = {}
+    if design == "zavizen":
+        with ClockSampler() as clocks:
+            for name, z in RENADRA_SIZES.items():
+                sizes[name] = {"zavizen": measure(zavizen_config(z, layers)),
+                               "renadra": measure(renadra_config(z, layers)),
+                               "kernels": zavizen_kernels_alone(z)}
+        head = sizes["4k"]["zavizen"]
+        line = {"metric": "decode tok/s at batch 8 of four Zavizen layers (width 4,096, B200); prefill, a smaller size, "
+                          "Renadra layers of equal size and Zavizen's kernels alone, each beside the like kernel of "
+                          "another design, alongside",
+                "value": head["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": head["decode_ms"], "higher_is_better": True, "dtype": "bf16",
+                "data": "synthetic (seeded uniform token ids, seeded random weights)",
+                "config": {"model": "Zavizen", "layers": layers, "sizes": RENADRA_SIZES, "streams": ZAVIZEN_STREAMS,
+                           "vocab": SUKALORN_VOCAB, "global_batch": batch, "prompt_len": PROMPT_LEN,
+                           "prefill_tokens": PREFILL_TOKENS, "page_size": args.page_size,
+                           "l2": "whole steps: inputs larger than L2; kernels alone: L2 flushed (a 256 MB write) before "
+                                 "every timed launch", "peaks": peaks["source"], "fp32_fma_tflops": FP32_FMA_TFLOPS},
+                "gpu_launches": head["launches_per_decode_step"] * args.steps, "sizes": sizes,
+                "clocks": clocks.summary()}
+        print(json.dumps(line))
+        return 0
     if design == "renadra":
         with ClockSampler() as clocks:
             for name, z in RENADRA_SIZES.items():
@@ -991,18 +1165,19 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page (a power of two, 16 or more)")
-    parser.add_argument("--shape", choices=sorted(SHAPES) + ["renadra", "sukalorn", "zifuzen"], default="8b",
+    parser.add_argument("--shape", choices=sorted(SHAPES) + ["renadra", "sukalorn", "zavizen", "zifuzen"], default="8b",
                         help="8b: the headline benchmark; 14b: a mixed scheduler load of 64 requests; 32b: long-context "
                              "decode at batch 16; sukalorn: prefill and decode of the Sukalorn design at two layer "
                              "sizes beside Qwen3 layers of equal size; zifuzen: the same for the Zifuzen design; renadra: the Renadra design beside "
-                             "Zifuzen layers of equal size (each prints its own one line)")
+                             "Zifuzen layers of equal size; zavizen: the Zavizen design beside Renadra layers of equal "
+                             "size (each prints its own one line)")
     parser.add_argument("--layers", type=int, default=None,
                         help="run fewer layers of the same sizes (reported in config beside the full count)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
     args = parser.parse_args()
 
-    if args.shape in ("renadra", "sukalorn", "zifuzen"):
+    if args.shape in ("renadra", "sukalorn", "zavizen", "zifuzen"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference arm runs the 8b shape only"}))
             return 0

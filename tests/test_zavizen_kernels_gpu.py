@@ -34,7 +34,8 @@ def _rand(shape, seed, scale=1.0):
 # ----------------------------------------------------------------------------- the stream in several copies
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("streams,width,y_float", [(1, 40, True), (3, 72, False), (4, 256, True), (8, 1031, False)])
+@pytest.mark.parametrize("streams,width,y_float", [(1, 40, True), (3, 72, False), (4, 256, True), (8, 1031, False),
+                                                   (2, 2048, False), (5, 4100, True)])
 def test_hyper_step_collapse_and_expand(dtype, streams, width, y_float):
     ops = _ops()
     n, eps = 13, 1e-5
