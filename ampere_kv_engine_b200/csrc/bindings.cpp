@@ -1311,7 +1311,7 @@ void rotary_prep(const Tensor& x, const Tensor& positions, const OptTensor& slot
                  const OptTensor& k_cache, const OptTensor& v_cache, int64_t num_heads, int64_t num_kv_heads,
                  int64_t head_dim, int64_t v_dim, int64_t rotary_dims, int64_t layout, double factor,
                  bool value_from_key, bool value_norm, double eps, const OptTensor& status, const OptTensor& q_norm,
-                 const OptTensor& k_norm, double row_norm_eps) {
+                 const OptTensor& k_norm, double row_norm_eps, int64_t x_off) {
   check_cuda(x, "x");
   check_cuda(q_out, "q_out");
   check_same(x, q_out, "x", "q_out");
@@ -1320,14 +1320,15 @@ void rotary_prep(const Tensor& x, const Tensor& positions, const OptTensor& slot
             "rotary_prep: rotary_dims must be even and at most the head's width; layout 0 or 1");
   AKV_CHECK(!value_from_key || v_dim == head_dim, "rotary_prep: a value that is its key has the key's width");
   const int64_t width = (num_heads + num_kv_heads) * head_dim + (value_from_key ? 0 : num_kv_heads * v_dim);
-  AKV_CHECK(x.dim() == 2 && x.size(1) == width, "x must be [tokens, ", width, "]: the q, k (and v) columns");
+  AKV_CHECK(x.dim() == 2 && x_off >= 0 && x.size(1) >= x_off + width,
+            "x must hold the ", width, " q, k (and v) columns of a token from column x_off on");
   const int64_t n = x.size(0);
   check_i32(positions, "positions", n);
   check_f32(freq, "freq", rotary_dims / 2);
   AKV_CHECK(q_out.numel() == n * num_heads * head_dim, "q_out must be [tokens, heads * head_dim]");
   akv::RotaryPrepParams p{};
-  p.x = x.data_ptr();
-  p.x_stride = width;
+  p.x = static_cast<const char*>(x.data_ptr()) + x_off * x.element_size();
+  p.x_stride = x.size(1);
   p.positions = positions.data_ptr<int>();
   p.freq = freq.data_ptr<float>();
   p.q_out = q_out.data_ptr();
@@ -1920,7 +1921,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("head_dim"), py::arg("v_dim"), py::arg("rotary_dims"), py::arg("layout"), py::arg("factor") = 1.0,
         py::arg("value_from_key") = false, py::arg("value_norm") = false, py::arg("eps") = 0.0,
         py::arg("status") = py::none(), py::arg("q_norm") = py::none(), py::arg("k_norm") = py::none(),
-        py::arg("row_norm_eps") = 0.0);
+        py::arg("row_norm_eps") = 0.0, py::arg("x_off") = 0);
   m.def("pair_rows_add", &pair_rows_add, py::arg("hidden"), py::arg("ids"), py::arg("sampled"), py::arg("positions"),
         py::arg("cu_q"), py::arg("state_slots"), py::arg("last_token"), py::arg("table"), py::arg("vocab"),
         py::arg("buckets"), py::arg("mul_prev"), py::arg("mul_cur"));

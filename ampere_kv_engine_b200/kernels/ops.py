@@ -963,18 +963,20 @@ ROTARY_LAYOUTS = {"half": 0, "pairs": 1}
 
 def rotary_prep(x, positions, slots, freq, k_cache, v_cache, *, num_heads, num_kv_heads, head_dim, v_dim, rotary_dims,
                 layout: str, factor: float = 1.0, value_from_key: bool = False, value_norm: bool = False,
-                eps: float = 0.0, status=None, q_norm=None, k_norm=None, row_norm_eps: float = 0.0) -> torch.Tensor:
+                eps: float = 0.0, status=None, q_norm=None, k_norm=None, row_norm_eps: float = 0.0,
+                x_off: int = 0) -> torch.Tensor:
     """From one product ``x`` [tokens, q heads | k heads (| v heads)]: the first ``rotary_dims`` dims of every q and k
     head turned by ``positions[t] * freq[i]`` (``layout`` ``"half"``: dim i pairs with i + rotary_dims / 2;
     ``"pairs"``: dim 2i with 2i + 1; cos and sin times ``factor``); the value is the v head (divided by its root mean
     square with ``value_norm``), or with ``value_from_key`` the k head before the turn (no v columns then); k and v go
     to their cache slots.  With ``q_norm`` / ``k_norm`` (float32 [heads * head_dim] / [kv heads * head_dim]) the whole q
     row and the whole k row are first divided by their root mean square over all heads (``row_norm_eps`` inside the
-    root) and multiplied by these weights.  Returns q [tokens, heads * head_dim]."""
+    root) and multiplied by these weights.  With ``x_off`` the q, k (and v) columns begin at that column of a wider
+    ``x`` (a product shared with another mixer).  Returns q [tokens, heads * head_dim]."""
     q_out = torch.empty((x.shape[0], num_heads * head_dim), dtype=x.dtype, device=x.device)
     ext().rotary_prep(x, positions, slots, freq, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim, v_dim,
                       int(rotary_dims), ROTARY_LAYOUTS[layout], float(factor), bool(value_from_key), bool(value_norm),
-                      float(eps), status, q_norm, k_norm, float(row_norm_eps))
+                      float(eps), status, q_norm, k_norm, float(row_norm_eps), int(x_off))
     _launched()
     return q_out
 

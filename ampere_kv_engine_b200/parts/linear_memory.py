@@ -195,15 +195,23 @@ class Retention(_LinearMemory):
         self.w_in = torch.cat([tensors[n[k]] for k in ("q", "k", "v", "gate")], dim=0).contiguous()   # [q | k | v | g]
         self.w_o = tensors[n["out"]].contiguous()
 
-    def heads_forward(self, x, ctx, cache):
+    def in_projection(self):
+        return self.w_in, None
+
+    def heads_forward(self, x, ctx, cache, projected=None):
+        """``projected``: (a product that holds this mixer's q, k, v and gate columns, the column where they begin)."""
         if cache.state is None:
             raise ValueError("retention: the cache manager gave this position no state")
-        x = ops.linear(x, self.w_in, status=ctx.status)
+        if projected is not None:
+            x, off = projected
+        else:
+            x, off = ops.linear(x, self.w_in, status=ctx.status), 0
         rows = ops.rotary_rows(x, ctx.positions, self.freq, num_heads=self.num_heads, head_dim=self.head_dim,
-                               v_dim=self.v_dim, rotary_dims=self.rotary_dims, q_off=0, k_off=self.qk_width,
-                               v_off=2 * self.qk_width, k_scale=self.key_scale)
+                               v_dim=self.v_dim, rotary_dims=self.rotary_dims, q_off=off, k_off=off + self.qk_width,
+                               v_off=off + 2 * self.qk_width, k_scale=self.key_scale)
         o = ops.linear_scan(rows, cache.state, ctx.cu_q, ctx.state_slots, num_heads=self.num_heads,
                             head_dim=self.head_dim, v_dim=self.v_dim, mode="plain_decay", q_off=0,
                             k_off=self.qk_width, v_off=2 * self.qk_width, decay=self.decay)
         return ops.group_norm_gate(o, None, group=self.v_dim, eps=self.norm_eps, out_dtype=x.dtype,
-                                   factor=self.out_scale, x=x, gate_off=2 * self.qk_width + self.v_width, gate="silu")
+                                   factor=self.out_scale, x=x, gate_off=off + 2 * self.qk_width + self.v_width,
+                                   gate="silu")

@@ -38,6 +38,8 @@ class ParallelMixers(Mixer):
         self.scales = (float(p.get("left_scale", 1.0)), float(p.get("right_scale", 1.0)))
         self.out_norm = dict(p["out_norm"]) if p.get("out_norm") else None
         self.norm_weights = None
+        self.w_in = None            # both sides' first projections as one matrix (made at the first step), or False
+        self.in_split = 0
         sides = []
         for side, scale in zip((p["left"], p["right"]), self.scales):
             if not isinstance(side, PartSpec):
@@ -93,11 +95,29 @@ class ParallelMixers(Mixer):
         if self.out_norm is not None:
             self.norm_weights = tuple(tensors[self.out_norm[side]].float().contiguous() for side in ("left", "right"))
 
+    def _projected(self, x, ctx):
+        """One product for both sides' first projections, where both sides take theirs from a shared product and
+        neither has a bias there: ((product, first column of the left side's), (product, first column of the
+        right side's)), else (None, None)."""
+        if self.w_in is None:
+            self.w_in = False
+            if all(hasattr(m, "in_projection") and hasattr(m, "heads_forward") and hasattr(m, "out_projection")
+                   and m.out_projection()[1] is None and m.in_projection()[1] is None for m in self.sides):
+                self.w_in = torch.cat([m.in_projection()[0] for m in self.sides], dim=0).contiguous()
+                self.in_split = self.sides[0].in_projection()[0].shape[0]
+                # the sides keep views of the one matrix, not copies of their parts
+                self.sides[0].w_in, self.sides[1].w_in = self.w_in[:self.in_split], self.w_in[self.in_split:]
+        if self.w_in is False:
+            return None, None
+        both = ops.linear(x, self.w_in, status=ctx.status)
+        return (both, 0), (both, self.in_split)
+
     @staticmethod
-    def _float_output(side, x, ctx, cache):
+    def _float_output(side, x, ctx, cache, projected=None):
         """A side's output in float32: its last product's accumulators where the side lets us run that product."""
         if hasattr(side, "heads_forward") and hasattr(side, "out_projection") and side.out_projection()[1] is None:
-            heads = side.heads_forward(x, ctx, cache)
+            heads = (side.heads_forward(x, ctx, cache, projected=projected) if projected is not None
+                     else side.heads_forward(x, ctx, cache))
             return ops.linear(heads, side.out_projection()[0], out_dtype=torch.float32, status=ctx.status)
         return side.forward(x, ctx, cache).float()
 
@@ -115,7 +135,8 @@ class ParallelMixers(Mixer):
         left, right = self.sides
         cl, cr = self._views(cache)
         if self.out_norm is not None:
-            return ops.normed_pair_sum(self._float_output(left, x, ctx, cl), self._float_output(right, x, ctx, cr),
+            pl, pr = self._projected(x, ctx)
+            return ops.normed_pair_sum(self._float_output(left, x, ctx, cl, pl), self._float_output(right, x, ctx, cr, pr),
                                        *self.norm_weights, eps=float(self.out_norm["eps"]), sa=self.scales[0],
                                        sb=self.scales[1], out_dtype=torch.float32)
         if self.joined:

@@ -149,18 +149,28 @@ class RotaryAttention(Mixer):
             self.q_norm = tensors[n["q_norm"]].float().contiguous()
             self.k_norm = tensors[n["k_norm"]].float().contiguous()
 
-    def heads_forward(self, x, ctx, cache) -> torch.Tensor:
-        """Everything before the output projection: [tokens, heads * v_dim], each head's output times ``out_scale``."""
+    def in_projection(self) -> tuple[torch.Tensor, torch.Tensor | None]:
+        """The matrix (and bias) of the one product that makes q, k (and v): a mixer that runs beside another one on
+        the same input may have it computed together with the other's and handed in as ``projected``."""
+        return self.w_in, self.b_in
+
+    def heads_forward(self, x, ctx, cache, projected=None) -> torch.Tensor:
+        """Everything before the output projection: [tokens, heads * v_dim], each head's output times ``out_scale``.
+        ``projected``: (a product that holds this mixer's q, k (and v) columns, the column where they begin)."""
         group = ctx.groups[cache.group]
         k_cache, v_cache = cache.tensors["k"], cache.tensors["v"]
         if not cache.writes:
             raise ValueError("rotary_attention: the mixer writes its own pages")
-        x = ops.linear(x, self.w_in, self.b_in, status=ctx.status)
+        if projected is not None:
+            x, x_off = projected
+        else:
+            x, x_off = ops.linear(x, self.w_in, self.b_in, status=ctx.status), 0
         q = ops.rotary_prep(x, ctx.positions, group.slot_mapping, self.freq, k_cache, v_cache,
                             num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
                             v_dim=self.v_dim, rotary_dims=self.rotary_dims, layout=self.layout, factor=self.factor,
                             value_from_key=self.value_from_key, value_norm=self.value_norm, eps=self.norm_eps,
-                            status=ctx.status, q_norm=self.q_norm, k_norm=self.k_norm, row_norm_eps=self.norm_eps)
+                            status=ctx.status, q_norm=self.q_norm, k_norm=self.k_norm, row_norm_eps=self.norm_eps,
+                            x_off=x_off)
         out = torch.empty((q.shape[0], self.num_heads * self.v_dim), dtype=q.dtype, device=q.device)
         run_attention(ctx, group, q, k_cache, v_cache, out, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
                       v_dim=self.v_dim, scale=self.scale, window=self.window, softcap=self.softcap,

@@ -373,9 +373,9 @@ class FakeExt:
 
     def rotary_prep(self, x, positions, slots, freq, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim, v_dim,
                     rotary_dims, layout, factor=1.0, value_from_key=False, value_norm=False, eps=0.0, status=None,
-                    q_norm=None, k_norm=None, row_norm_eps=0.0):
+                    q_norm=None, k_norm=None, row_norm_eps=0.0, x_off=0):
         n = x.shape[0]
-        xf = x.float()
+        xf = x.float()[:, x_off:]
         a, b = num_heads * head_dim, num_kv_heads * head_dim
         q_row, k_row = xf[:, :a], xf[:, a:a + b]
         k_plain = k_row.view(n, num_kv_heads, head_dim)
@@ -404,7 +404,7 @@ class FakeExt:
         if value_from_key:
             v = k_plain
         else:
-            v = xf[:, a + b:].view(n, num_kv_heads, v_dim)
+            v = xf[:, a + b:a + b + num_kv_heads * v_dim].view(n, num_kv_heads, v_dim)
             if value_norm:
                 v = v * torch.rsqrt(v.square().mean(-1, keepdim=True) + eps)
         page_size = k_cache.shape[2]
