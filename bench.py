@@ -656,12 +656,22 @@ def sukalorn_shape(args, design: str = "sukalorn") -> int:
         decode_ms = timed(one, args.steps)
         launches = ops.launch_count // args.steps
         runner.raise_on_status()
-        weights = sum(t.numel() * t.element_size() for part in engine.model._parts() for t in vars(part).values()
-                      if isinstance(t, torch.Tensor) and t.dim() >= 2)
+        def matrix_bytes(parts):
+            """Bytes of the parts' matrices, a matrix that several parts hold views of counted once."""
+            seen, total = set(), 0
+            for part in parts:
+                for t in vars(part).values():
+                    if isinstance(t, torch.Tensor) and t.dim() >= 2:
+                        storage = t.untyped_storage()
+                        if storage.data_ptr() not in seen:
+                            seen.add(storage.data_ptr())
+                            total += storage.nbytes()
+            return total
+
+        weights = matrix_bytes(engine.model._parts())
         # without the tables a step only gathers rows of (token and pair embeddings): what a decode step reads whole
         from ampere_kv_engine_b200.parts.embedding import Embedding
-        read = sum(t.numel() * t.element_size() for part in engine.model._parts() if not isinstance(part, Embedding)
-                   for t in vars(part).values() if isinstance(t, torch.Tensor) and t.dim() >= 2)
+        read = matrix_bytes(part for part in engine.model._parts() if not isinstance(part, Embedding))
         del engine, runner, seqs
         torch.cuda.empty_cache()
         return {"prefill_ms": round(prefill_ms, 3), "prefill_tok_s": round(PREFILL_TOKENS / prefill_ms * 1000, 1),
