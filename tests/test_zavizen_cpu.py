@@ -69,13 +69,13 @@ def test_spec_schedules_the_loop_and_gives_layers_their_parts():
             "l0.mlp.router", "l0.mlp.shared.up", "l1.mix.left.q.norm", "l1.mix.left.k.norm", "l1.mix.left.out",
             "l1.mix.right.out", "l1.mix.right.g", "l1.mlp.gate", "l3.mlp.e3.gate"} <= wanted
     assert not ({"l3.mlp.shared.up", "l2.mlp.gate", "l1.mix.right.norm"} & set(specs)) and specs["l2.hc2.mix"].optional
-    assert specs["l0.mix.in"].shape == (2 * 48 + 2 * 2 * 20 + 4, 72) and specs["l0.mix.conv"].shape == (48 + 80, 4)
+    assert specs["l0.mix.in"].shape == (2 * 48 + 2 * 2 * 20 + 4, 72) and specs["l0.mix.conv"].shape == (48 + 80, 3)
     assert specs["l1.mix.left.q.norm"].shape == (96,) and specs["l1.mix.left.k.norm"].shape == (48,)
     assert specs["l0.hc1.mix"].shape == (3, 3) and specs["l1.mix.left.o"].shape == (72, 64)
     caches = model.cache_specs()
     assert len(caches) == len(spec.schedule)
     memory = ops.linear_scan_state_floats(4, 20, 12)
-    assert caches[0].kind == "none" and caches[0].state_shape == ((memory + 3 * 128 + 3) // 4 * 4,)
+    assert caches[0].kind == "none" and caches[0].state_shape == ((memory + 2 * 128 + 3) // 4 * 4,)
     assert caches[1].kind == "full" and caches[1].state_shape == (ops.linear_scan_state_floats(3, 12, 20),)
     assert [t.width for t in caches[1].stored()] == [24, 16]
     # the two appearances of a parallel layer have a cache each in one group

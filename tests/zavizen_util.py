@@ -3,7 +3,7 @@ never committed) and the plain implementation's logits.
 
 The configurations differ from one another in every size, in the order of their layers and in what is present:
 
-* ``Z1``: a state-space layer first (four heads on two groups, four taps, two norm groups) with six experts in three
+* ``Z1``: a state-space layer first (four heads on two groups, three taps, two norm groups) with six experts in three
   groups of which two are kept and a shared expert; then two parallel layers (values narrower than keys and as wide;
   two and one query heads per key head; rotation over part of a head with scaled frequencies and over all of it
   without) of which one has a dense feed-forward and one none; a state-space layer with one group, two taps and four
@@ -72,7 +72,7 @@ Z1 = {
     "architecture": "Zavizen", "vocab": 193, "width": 72, "norm": {"eps": 1e-5}, "streams": 3,
     "loop": {"start": 1, "stop": 3, "times": 2},
     "layers": [
-        _layer("mamba2", _mamba(4, 12, 20, 2, 4, 2), _moe(6, 2, 24, 2.0, groups=(3, 2), shared=40)),
+        _layer("mamba2", _mamba(4, 12, 20, 2, 3, 2), _moe(6, 2, 24, 2.0, groups=(3, 2), shared=40)),
         _layer("parallel", _parallel((4, 2, 24, 16, 0.2, _rot(16, 500.0, 2.0)),
                                      (3, 12, 20, (0.5, 0.93, 0.999), _rot(12, 100.0))), _dense(96)),
         _layer("parallel", _parallel((3, 3, 16, 16, 0.25, _rot(8, 10000.0)),
@@ -95,7 +95,7 @@ Z3 = {
     "layers": [
         _layer("parallel", _parallel((8, 2, 128, 128, 0.09, _rot(64, 1000000.0, 4.0)),
                                      (4, 64, 32, (0.7, 0.9, 0.99, 1.0), _rot(64, 10000.0))), _dense(384)),
-        _layer("mamba2", _mamba(4, 64, 128, 1, 4, 2), _moe(8, 2, 128, 1.5, groups=(2, 1), shared=64)),
+        _layer("mamba2", _mamba(4, 64, 128, 1, 4, 2), _moe(8, 3, 128, 1.25, groups=(4, 2), shared=64)),
         _layer("parallel", _parallel((2, 1, 64, 64, 0.125, _rot(32, 10000.0)), (2, 128, 64, (0.95, 0.999), _rot(16, 100.0))),
                _moe(16, 4, 64, 2.5, groups=(4, 2))),
     ],
