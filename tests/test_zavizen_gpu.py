@@ -94,6 +94,22 @@ def test_replay_matches_plain(name, mode, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", ["last32", "mixed"])
+def test_a_width_at_which_clusters_share_a_row(mode, dtype):
+    """Steps of few tokens at width 512: the blocks of a row's cluster add up their sums through distributed shared
+    memory, eagerly and inside captured steps."""
+    raw, page = zu.CONFIGS["Z4"]
+    folder = zu.model_folder("Z4")
+    requests = _requests(folder, raw, (1, 2, 19, 47, 70), 13, dtype)
+    expected = zu.plain_logits(folder, raw, requests)
+    trace = _trace(mode, requests, 64 * 4)
+    outputs, engine = ru.run_on_device(folder, dtype, trace, 64 * 4, page_size=page, max_seqs=4)
+    _check(trace, outputs, expected, dtype)
+    if mode == "last32":
+        assert engine.runner.graph_replays > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["Z1", "Z3"])
 def test_decoding_from_the_first_token(name, dtype):
     """Every token a step of its own for 150 positions: the keys were written one at a time over several pages, and

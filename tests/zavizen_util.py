@@ -13,6 +13,9 @@ The configurations differ from one another in every size, in the order of their 
 * ``Z3``: sizes at which the 16-byte paths, the tensor-core attention kernels and the small-batch product kernel run:
   attention heads of 128, memories of 64 x 32 and 128 x 64, experts with widths that are multiples of eight; the
   whole model is one loop run twice; four copies of the stream.
+* ``Z4``: a width at which the row-wise kernels share a row among the blocks of a cluster on steps of few tokens
+  (the stream's write, read and norm; the two normed outputs; the norms over whole q and k rows; the state-space
+  preparation cut over channels): width 512, ten q and k heads, 512 convolved channels.
 
 The folders' tensors are made so that mechanisms matter: copies of the stream mix mostly with themselves, routers are
 scaled up so that choices vary and are rarely close, step biases spread so that some state-space heads keep their
@@ -100,7 +103,15 @@ Z3 = {
                _moe(16, 4, 64, 2.5, groups=(4, 2))),
     ],
 }
-CONFIGS = {"Z1": (Z1, 16), "Z2": (Z2, 32), "Z3": (Z3, 16)}
+Z4 = {
+    "architecture": "Zavizen", "vocab": 150, "width": 512, "norm": {"eps": 1e-6}, "streams": 2,
+    "layers": [
+        _layer("parallel", _parallel((8, 2, 32, 32, 0.2, _rot(16, 10000.0, 2.0)), (2, 32, 48, (0.9, 0.99), _rot(32, 500.0))),
+               _dense(128)),
+        _layer("mamba2", _mamba(4, 96, 32, 2, 4, 1), _moe(4, 2, 64, 1.0, shared=32)),
+    ],
+}
+CONFIGS = {"Z1": (Z1, 16), "Z2": (Z2, 32), "Z3": (Z3, 16), "Z4": (Z4, 16)}
 
 
 def config(name: str) -> dict:
